@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts.base import BuildEnv, KVCacheNeed, KVView, LayerContext, StateNeed
+from ..parts.base import BuildEnv, CompositeNeed, KVCacheNeed, KVView, LayerContext, StateNeed
 from .manager import CacheManager, GroupSpec
 
 
@@ -34,12 +34,19 @@ class CacheStorage:
         self.group_specs: List[GroupSpec] = []
         self._group_layers: List[int] = []
         self._group_shape: List[Tuple[int, int]] = []
-        self.entry_place: Dict[int, Tuple[int, int]] = {}      # schedule index -> (group, layer in group)
-        self._state_needs: Dict[int, StateNeed] = {}
-        for index, need in enumerate(needs):
+        self.entry_place: Dict[Tuple, Tuple[int, int]] = {}    # key of a need -> (group, layer in group)
+        self._state_needs: Dict[Tuple, StateNeed] = {}
+        self._composite: Dict[Tuple, Tuple[str, ...]] = {}     # key of a composite need -> its children's names
+
+        def register(key: Tuple, need) -> None:
+            """``key``: (schedule index,) for a run's own need, (schedule index, child, ...) below a composite one."""
             if need is None:
-                continue
-            if isinstance(need, KVCacheNeed):
+                return
+            if isinstance(need, CompositeNeed):
+                self._composite[key] = tuple(name for name, _ in need.children)
+                for name, child in need.children:
+                    register(key + (name,), child)
+            elif isinstance(need, KVCacheNeed):
                 sig = (need.window, need.num_kv_heads, need.head_dim)
                 if sig not in signature_to_group:
                     signature_to_group[sig] = len(self.group_specs)
@@ -53,12 +60,15 @@ class CacheStorage:
                     self._group_layers.append(0)
                     self._group_shape.append((need.num_kv_heads, need.head_dim))
                 g = signature_to_group[sig]
-                self.entry_place[index] = (g, self._group_layers[g])
+                self.entry_place[key] = (g, self._group_layers[g])
                 self._group_layers[g] += 1
             elif isinstance(need, StateNeed):
-                self._state_needs[index] = need
+                self._state_needs[key] = need
             else:
-                raise TypeError(f"schedule entry {index}: unknown cache need {need!r}")
+                raise TypeError(f"schedule entry {key[0]}: unknown cache need {need!r}")
+
+        for index, need in enumerate(needs):
+            register((index,), need)
         if not self.group_specs:
             # a model without paged layers still counts tokens per request
             self.group_specs.append(GroupSpec("none", page_size, num_pages, None))
@@ -66,7 +76,7 @@ class CacheStorage:
             self._group_shape.append((0, 0))
         self.pools: List[Optional[torch.Tensor]] = []
         self._layer_views: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
-        self.states: Dict[int, torch.Tensor] = {}
+        self.states: Dict[Tuple, torch.Tensor] = {}
 
     def make_manager(self) -> CacheManager:
         manager = CacheManager(self.group_specs, self.max_reside)
@@ -104,8 +114,11 @@ class CacheStorage:
             t[slot].zero_()                  # in stream order: after the last step of whoever held the slot before
 
     def layer_context(self, owner_index: int, batch, write: bool) -> LayerContext:
+        return self._context((owner_index,), batch, write)
+
+    def _context(self, key: Tuple, batch, write: bool) -> LayerContext:
         ctx = LayerContext(batch=batch, write_cache=write)
-        place = self.entry_place.get(owner_index)
+        place = self.entry_place.get(key)
         if place is not None:
             g, layer = place
             views = self._layer_views.get(place)
@@ -114,6 +127,9 @@ class CacheStorage:
                 views = self._layer_views[place] = (pool[layer, 0], pool[layer, 1])
             ctx.kv = KVView(k=views[0], v=views[1], block_table=batch.block_tables[g],
                             page_size=self.group_specs[g].page_size)
-        if owner_index in self.states:
-            ctx.state = self.states[owner_index]
+        if key in self.states:
+            ctx.state = self.states[key]
+        names = self._composite.get(key)
+        if names is not None:
+            ctx.children = {name: self._context(key + (name,), batch, write) for name in names}
         return ctx

@@ -12,7 +12,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass
-from typing import Callable, Dict
+from typing import Callable, Dict, Optional
 
 
 @dataclass(frozen=True)
@@ -25,6 +25,9 @@ class Architecture:
     ignorable_tensors: Callable = lambda cfg: set()
     # rows of each checkpoint tensor inside a fused parameter, or None for an even split
     split_rows: Callable = lambda cfg, param: None
+    # checkpoint tensor -> (shape, law of random values), for an architecture whose checkpoint layout is not the
+    # parameters' cut into equal or ``split_rows`` pieces (padded heads, tensors of many kinds); None: derived
+    checkpoint_shapes: Optional[Callable] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -44,7 +47,9 @@ def architectures():
 
 def resolve(raw_config: dict) -> Architecture:
     """The architecture a config.json (as a dict) asks for."""
-    names = raw_config.get("architectures") or []
+    names = list(raw_config.get("architectures") or [])
+    if isinstance(raw_config.get("architecture"), str):      # a config.json that names one architecture, as a string
+        names.append(raw_config["architecture"])
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]
@@ -64,6 +69,8 @@ def read_config(model_dir: str):
     with open(path) as f:
         raw = json.load(f)
     arch = resolve(raw)
+    if hasattr(arch.config_cls, "from_model_dir"):       # sizes that only the tensors' shapes give
+        return arch, arch.config_cls.from_model_dir(model_dir, raw)
     return arch, arch.config_cls.from_dict(raw)
 
 
@@ -74,6 +81,12 @@ def _register_builtin() -> None:
         name="Qwen3ForCausalLM", model_type="qwen3", config_cls=Qwen3Config,
         decoder_spec=qwen3.decoder_spec, weight_sources=qwen3.weight_sources,
         ignorable_tensors=qwen3.ignorable_tensors, split_rows=qwen3.split_rows))
+    from ..models import pisatar
+    from .pisatar_config import PisatarConfig
+    register_architecture(Architecture(
+        name="Pisatar", model_type="pisatar", config_cls=PisatarConfig,
+        decoder_spec=pisatar.decoder_spec, weight_sources=pisatar.weight_sources,
+        ignorable_tensors=pisatar.ignorable_tensors, checkpoint_shapes=pisatar.checkpoint_shapes))
 
 
 _register_builtin()

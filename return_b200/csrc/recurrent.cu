@@ -1,0 +1,477 @@
+// Kernels of the mixers that carry a matrix state per head instead of cached keys: linear attention with a
+// fixed decay (retention), the gated delta rule with a decay per key channel, and the matrix memory with
+// exponential gates; plus the elementwise steps around them.
+//
+// A head's state S is a [D, V] matrix in float32 that is read out as o = S^T q.  One token's update is
+//     fixed decay:     S <- a S + k v^T                                   o = S^T q
+//     delta rule:      S <- g * S (row i by g_i);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+//     matrix memory:   m' = max(f + m, i);  a = exp(f + m - m'),  b = exp(i - m');
+//                      S <- a S + b k v^T;  n <- a n + b k;  o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+// All of it is float32 whatever the activation type is.  The scan kernel walks the tokens of a segment in order,
+// one after the other, for prompts and single tokens alike: a token's result therefore does not depend on how a
+// prompt was cut into steps or on what else is in the batch (the sums have one fixed order).
+//
+// Thread layout of the scan: a CTA of 256 threads owns 32 value columns of one head of one segment.  Eight
+// neighbouring lanes share a column and split its D rows between them (lane r holds rows r, r + 8, ...), so a
+// column's dot products end with three shuffles.  The state of a request lives in its slot in the same order,
+// [head][row / 8][column][row % 8], which makes a warp's loads and stores of it whole 128-byte lines.
+#include "common.cuh"
+
+#define SCAN_THREADS 256
+#define SCAN_COLS 32          // value columns of a CTA
+#define SCAN_TC 8             // tokens staged in shared memory at a time
+
+#define MODE_DECAY 0
+#define MODE_MEMORY 1
+#define MODE_DELTA 2
+
+struct ScanArgs {
+    const void* q; const void* k; const void* v;        // (t, head, i) at base + t * ld + head * dim + i
+    int q_ld, k_ld, v_ld;
+    int q_f32, k_f32, v_f32;                            // 1: float32, 0: bfloat16
+    const float* gate_a;      // decay: [H] decays; memory: [T, 2H] gate pre-activations (input, forget); delta: [T, H*D] row decays
+    const float* gate_b;      // memory: [2H] gate biases; delta: [T, H] beta
+    float cap, q_scale;
+    float* state;             // [slots, state_stride]
+    long long state_stride;
+    int s_off, n_off, m_off;  // where S, n and m start inside a slot's row
+    const int* cu_q; const int* seg_slot;
+    float* out;               // [T, H*V]
+    int H, G, D, V;
+};
+
+__device__ __forceinline__ float ld_elem(const void* p, int f32, size_t i) {
+    return f32 ? ((const float*)p)[i] : __bfloat162float(((const bf16*)p)[i]);
+}
+
+__device__ __forceinline__ float group8_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float logsigmoid_f(float x) { return x < 0.f ? x - log1pf(expf(x)) : -log1pf(expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+template <int MODE, int NR>
+__global__ void __launch_bounds__(SCAN_THREADS)
+linear_scan_kernel(const ScanArgs a) {
+    constexpr int DP = NR * 8;
+    __shared__ float sq[SCAN_TC][DP];
+    __shared__ float sk[SCAN_TC][DP];
+    __shared__ float sg[MODE == MODE_DELTA ? SCAN_TC : 1][DP];
+    __shared__ float sv[SCAN_TC][SCAN_COLS];
+    __shared__ float sa[SCAN_TC], sb[SCAN_TC];
+    const int seg = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * SCAN_COLS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = lane & 7, jj = warp * 4 + (lane >> 3), j = j0 + jj;
+    const int H = a.H, D = a.D, V = a.V;
+    const int kvh = h / (H / a.G);
+    const int nrd = (D + 7) >> 3;                      // row groups that exist
+    const int t0 = a.cu_q[seg], t1 = a.cu_q[seg + 1];
+    float* st = a.state + (long long)a.seg_slot[seg] * a.state_stride;
+    float* Sg = st + a.s_off + (size_t)h * nrd * 8 * V;
+    const bool col = j < V;
+
+    float S[NR], n[MODE == MODE_MEMORY ? NR : 1];
+    float m = 0.f;
+#pragma unroll
+    for (int ii = 0; ii < NR; ++ii) S[ii] = (col && ii < nrd) ? Sg[((size_t)ii * V + j) * 8 + r] : 0.f;
+    if (MODE == MODE_MEMORY) {
+#pragma unroll
+        for (int ii = 0; ii < NR; ++ii) n[ii] = ii < nrd ? st[a.n_off + (size_t)h * nrd * 8 + ii * 8 + r] : 0.f;
+        m = st[a.m_off + h];
+    }
+    const float decay = MODE == MODE_DECAY ? a.gate_a[h] : 0.f;
+
+    for (int tc = t0; tc < t1; tc += SCAN_TC) {
+        const int nt = min(SCAN_TC, t1 - tc);
+        __syncthreads();                               // the chunk before this one has been used
+        for (int e = tid; e < nt * DP; e += SCAN_THREADS) {
+            const int tt = e / DP, i = e - tt * DP;
+            const size_t t = (size_t)(tc + tt);
+            const bool live = i < D;
+            sq[tt][i] = live ? ld_elem(a.q, a.q_f32, t * a.q_ld + (size_t)kvh * D + i) * a.q_scale : 0.f;
+            sk[tt][i] = live ? ld_elem(a.k, a.k_f32, t * a.k_ld + (size_t)kvh * D + i) : 0.f;
+            if (MODE == MODE_DELTA) sg[tt][i] = live ? a.gate_a[(t * H + h) * D + i] : 1.f;
+        }
+        for (int e = tid; e < nt * SCAN_COLS; e += SCAN_THREADS) {
+            const int tt = e / SCAN_COLS, c = e - tt * SCAN_COLS;
+            sv[tt][c] = (j0 + c < V) ? ld_elem(a.v, a.v_f32, (size_t)(tc + tt) * a.v_ld + (size_t)h * V + j0 + c) : 0.f;
+        }
+        if (tid < nt) {
+            const size_t t = (size_t)(tc + tid);
+            if (MODE == MODE_MEMORY) {
+                const float xi = a.gate_a[t * 2 * H + h] + a.gate_b[h];
+                const float xf = a.gate_a[t * 2 * H + H + h] + a.gate_b[H + h];
+                sa[tid] = a.cap * tanhf(xi / a.cap);
+                sb[tid] = logsigmoid_f(a.cap * tanhf(xf / a.cap));
+            } else if (MODE == MODE_DELTA) {
+                sb[tid] = a.gate_b[t * H + h];
+            }
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float vj = sv[tt][jj];
+            float o = 0.f;
+            if (MODE == MODE_DECAY) {
+#pragma unroll
+                for (int ii = 0; ii < NR; ++ii) {
+                    S[ii] = fmaf(decay, S[ii], sk[tt][ii * 8 + r] * vj);
+                    o = fmaf(S[ii], sq[tt][ii * 8 + r], o);
+                }
+                o = group8_sum(o);
+            } else if (MODE == MODE_MEMORY) {
+                const float lf = sb[tt], li = sa[tt];
+                const float m_new = fmaxf(lf + m, li);
+                const float fa = expf(lf + m - m_new), fb = expf(li - m_new);
+                m = m_new;
+                float nq = 0.f;
+#pragma unroll
+                for (int ii = 0; ii < NR; ++ii) {
+                    const float bk = fb * sk[tt][ii * 8 + r], qi = sq[tt][ii * 8 + r];
+                    S[ii] = fmaf(fa, S[ii], bk * vj);
+                    n[ii] = fmaf(fa, n[ii], bk);
+                    o = fmaf(S[ii], qi, o);
+                    nq = fmaf(n[ii], qi, nq);
+                }
+                o = group8_sum(o);
+                nq = group8_sum(nq);
+                o = o / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
+            } else {
+                float kv = 0.f;
+#pragma unroll
+                for (int ii = 0; ii < NR; ++ii) {
+                    S[ii] *= sg[tt][ii * 8 + r];
+                    kv = fmaf(S[ii], sk[tt][ii * 8 + r], kv);
+                }
+                kv = group8_sum(kv);
+                const float u = sb[tt] * (vj - kv);
+#pragma unroll
+                for (int ii = 0; ii < NR; ++ii) {
+                    S[ii] = fmaf(sk[tt][ii * 8 + r], u, S[ii]);
+                    o = fmaf(S[ii], sq[tt][ii * 8 + r], o);
+                }
+                o = group8_sum(o);
+            }
+            if (r == 0 && col) a.out[((size_t)(tc + tt) * H + h) * V + j] = o;
+        }
+    }
+    if (col) {
+#pragma unroll
+        for (int ii = 0; ii < NR; ++ii)
+            if (ii < nrd) Sg[((size_t)ii * V + j) * 8 + r] = S[ii];
+    }
+    if (MODE == MODE_MEMORY && blockIdx.x == 0 && warp == 0 && lane < 8) {
+#pragma unroll
+        for (int ii = 0; ii < NR; ++ii)
+            if (ii < nrd) st[a.n_off + (size_t)h * nrd * 8 + ii * 8 + r] = n[ii];
+        if (lane == 0) st[a.m_off + h] = m;
+    }
+}
+
+template <int MODE>
+static int launch_scan(const ScanArgs& a, int segments, cudaStream_t st) {
+    if (segments <= 0) return 0;
+    if (a.D <= 0 || a.D > 256 || a.V <= 0 || a.G <= 0 || a.H % a.G) return (int)cudaErrorInvalidValue;
+    dim3 grid((a.V + SCAN_COLS - 1) / SCAN_COLS, a.H, segments);
+    if (a.D <= 32) linear_scan_kernel<MODE, 4><<<grid, SCAN_THREADS, 0, st>>>(a);
+    else if (a.D <= 64) linear_scan_kernel<MODE, 8><<<grid, SCAN_THREADS, 0, st>>>(a);
+    else if (a.D <= 128) linear_scan_kernel<MODE, 16><<<grid, SCAN_THREADS, 0, st>>>(a);
+    else linear_scan_kernel<MODE, 32><<<grid, SCAN_THREADS, 0, st>>>(a);
+    return rb_launch_status();
+}
+
+// mode: 0 fixed decay, 1 matrix memory, 2 delta rule.  The arguments are those of ScanArgs, in its order.
+RB_EXPORT int rb_linear_scan(int mode, const void* q, const void* k, const void* v, int q_ld, int k_ld, int v_ld,
+                             int q_f32, int k_f32, int v_f32, const float* gate_a, const float* gate_b, float cap,
+                             float q_scale, float* state, long long state_stride, int s_off, int n_off, int m_off,
+                             const int* cu_q, const int* seg_slot, float* out, int H, int G, int D, int V,
+                             int segments, cudaStream_t st) {
+    ScanArgs a;
+    a.q = q; a.k = k; a.v = v; a.q_ld = q_ld; a.k_ld = k_ld; a.v_ld = v_ld;
+    a.q_f32 = q_f32; a.k_f32 = k_f32; a.v_f32 = v_f32;
+    a.gate_a = gate_a; a.gate_b = gate_b; a.cap = cap; a.q_scale = q_scale;
+    a.state = state; a.state_stride = state_stride; a.s_off = s_off; a.n_off = n_off; a.m_off = m_off;
+    a.cu_q = cu_q; a.seg_slot = seg_slot; a.out = out; a.H = H; a.G = G; a.D = D; a.V = V;
+    if (mode == MODE_DECAY) return launch_scan<MODE_DECAY>(a, segments, st);
+    if (mode == MODE_MEMORY) return launch_scan<MODE_MEMORY>(a, segments, st);
+    if (mode == MODE_DELTA) return launch_scan<MODE_DELTA>(a, segments, st);
+    return (int)cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------- rotation of q and k into float32
+// x: two runs of `heads` heads of size D inside rows of a projection buffer (q at q_off, k at k_off).  The first
+// `rot` elements of a head turn by the angle of the token's position (tables cos, sin [positions, rot/2]), element
+// i paired with i + rot/2; k is then multiplied by k_scale.  Results go to q32, k32 [T, heads, D].
+template <typename TA>
+__global__ void rotary_to_f32_kernel(const TA* __restrict__ x, int ld, int q_off, int k_off,
+                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
+                                     const int* __restrict__ pos, float* __restrict__ q32, float* __restrict__ k32,
+                                     int heads, int D, float q_scale, float k_scale) {
+    const int t = blockIdx.x, hh = blockIdx.y;           // hh < heads: q, else k
+    const bool is_k = hh >= heads;
+    const int h = is_k ? hh - heads : hh;
+    const TA* src = x + (size_t)t * ld + (is_k ? k_off : q_off) + (size_t)h * D;
+    float* dst = (is_k ? k32 : q32) + ((size_t)t * heads + h) * D;
+    const float scale = is_k ? k_scale : q_scale;
+    const int half = rot >> 1;
+    const int p = pos[t];
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float y;
+        if (d < half) {
+            const float c = cos_t[(size_t)p * half + d], s = sin_t[(size_t)p * half + d];
+            y = to_f32(src[d]) * c - to_f32(src[d + half]) * s;
+        } else if (d < rot) {
+            const int i = d - half;
+            const float c = cos_t[(size_t)p * half + i], s = sin_t[(size_t)p * half + i];
+            y = to_f32(src[d]) * c + to_f32(src[i]) * s;
+        } else {
+            y = to_f32(src[d]);
+        }
+        dst[d] = y * scale;
+    }
+}
+
+RB_EXPORT int rb_rotary_to_f32(const void* x, int ld, int q_off, int k_off, const float* cos_t, const float* sin_t,
+                               int rot, const int* pos, float* q32, float* k32, int act_dtype, int T, int heads, int D,
+                               float q_scale, float k_scale, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (rot > D || (rot & 1)) return (int)cudaErrorInvalidValue;
+    dim3 grid(T, 2 * heads);
+    const int threads = D <= 32 ? 32 : D <= 64 ? 64 : 128;
+    if (act_dtype == RB_F32)
+        rotary_to_f32_kernel<float><<<grid, threads, 0, st>>>((const float*)x, ld, q_off, k_off, cos_t, sin_t, rot, pos,
+                                                             q32, k32, heads, D, q_scale, k_scale);
+    else
+        rotary_to_f32_kernel<bf16><<<grid, threads, 0, st>>>((const bf16*)x, ld, q_off, k_off, cos_t, sin_t, rot, pos,
+                                                            q32, k32, heads, D, q_scale, k_scale);
+    return rb_launch_status();
+}
+
+// ---------------------------------------------------------------- what the delta rule needs of a token
+// Units of work (blockIdx.y): G query heads, G key heads, H value heads, H rows of decays, one of betas.
+//   q, k, v: a short causal convolution over time per channel (taps [C, K], the last column is the current
+//   token's; what lies before the segment comes from the request's conv state, which holds the K - 1 inputs
+//   before it, oldest first, and is zero for a new request), then silu; q and k heads are then made unit
+//   vectors (x / sqrt(sum x^2 + 1e-6)), q also times q_scale.  Channels: q heads, k heads, v heads, in this order.
+//   decay[t, h, i] = exp(-exp(A_log[h]) * softplus(a[t, h, i] + dt_bias[h, i]))   (in place over a)
+//   beta[t, h] = sigmoid(b[t, h])                                                 (in place over b)
+template <typename TA>
+__global__ void __launch_bounds__(128)
+delta_prep_kernel(const TA* __restrict__ x, int ld, const void* __restrict__ taps, int taps_dtype, int K,
+                  const float* __restrict__ state, long long state_stride, int conv_off,
+                  const int* __restrict__ tok_seg, const int* __restrict__ cu_q, const int* __restrict__ seg_slot,
+                  float* __restrict__ q32, float* __restrict__ k32, float* __restrict__ v32,
+                  float* __restrict__ a, const void* __restrict__ A_log, const void* __restrict__ dt_bias, int vec_dtype,
+                  float* __restrict__ b, int H, int G, int D, int V, float q_scale) {
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, unit = blockIdx.y;
+    if (unit >= 2 * G + H) {
+        if (unit < 2 * G + 2 * H) {
+            const int h = unit - 2 * G - H;
+            const float rate = expf(load_as_f32(A_log, vec_dtype, h));
+            for (int i = threadIdx.x; i < D; i += blockDim.x) {
+                const size_t e = ((size_t)t * H + h) * D + i;
+                a[e] = expf(-rate * softplus_f(a[e] + load_as_f32(dt_bias, vec_dtype, (size_t)h * D + i)));
+            }
+        } else {
+            for (int h = threadIdx.x; h < H; h += blockDim.x) b[(size_t)t * H + h] = sigmoid_f(b[(size_t)t * H + h]);
+        }
+        return;
+    }
+    const int seg = tok_seg[t];
+    const int l = t - cu_q[seg];                          // tokens of this segment before t
+    const float* cs = state + (long long)seg_slot[seg] * state_stride + conv_off;
+    int c0, len;
+    float* dst;
+    if (unit < G) { c0 = unit * D; len = D; dst = q32 + ((size_t)t * G + unit) * D; }
+    else if (unit < 2 * G) { c0 = G * D + (unit - G) * D; len = D; dst = k32 + ((size_t)t * G + (unit - G)) * D; }
+    else { c0 = 2 * G * D + (unit - 2 * G) * V; len = V; dst = v32 + ((size_t)t * H + (unit - 2 * G)) * V; }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) {
+        const int c = c0 + i;
+        float y = 0.f;
+        for (int jb = K - 1; jb >= 0; --jb) {             // jb tokens back, oldest first
+            const float w = load_as_f32(taps, taps_dtype, (size_t)c * K + (K - 1 - jb));
+            const float xv = jb <= l ? to_f32(x[(size_t)(t - jb) * ld + c]) : cs[(size_t)c * (K - 1) + (K - 1 - (jb - l))];
+            y = fmaf(w, xv, y);
+        }
+        y = y / (1.0f + expf(-y));
+        dst[i] = y;
+        ss += y * y;
+    }
+    if (unit < 2 * G) {
+        ss = block_sum(ss, scratch);
+        const float inv = (unit < G ? q_scale : 1.0f) / sqrtf(ss + 1e-6f);
+        for (int i = threadIdx.x; i < len; i += blockDim.x) dst[i] *= inv;
+    }
+}
+
+RB_EXPORT int rb_delta_prep(const void* x, int ld, const void* taps, int taps_dtype, int K, const float* state,
+                            long long state_stride, int conv_off, const int* tok_seg, const int* cu_q, const int* seg_slot,
+                            float* q32, float* k32, float* v32, float* a, const void* A_log, const void* dt_bias,
+                            int vec_dtype, float* b, int act_dtype, int T, int H, int G, int D, int V, float q_scale,
+                            cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (K < 1) return (int)cudaErrorInvalidValue;
+    dim3 grid(T, 2 * G + 2 * H + 1);
+    if (act_dtype == RB_F32)
+        delta_prep_kernel<float><<<grid, 128, 0, st>>>((const float*)x, ld, taps, taps_dtype, K, state, state_stride, conv_off,
+            tok_seg, cu_q, seg_slot, q32, k32, v32, a, A_log, dt_bias, vec_dtype, b, H, G, D, V, q_scale);
+    else
+        delta_prep_kernel<bf16><<<grid, 128, 0, st>>>((const bf16*)x, ld, taps, taps_dtype, K, state, state_stride, conv_off,
+            tok_seg, cu_q, seg_slot, q32, k32, v32, a, A_log, dt_bias, vec_dtype, b, H, G, D, V, q_scale);
+    return rb_launch_status();
+}
+
+// The conv state after a step: the last K - 1 inputs of each channel, oldest first.  A segment shorter than K - 1
+// keeps the newest part of what the state held.  A thread reads all it needs of a channel before it writes.
+#define CONV_MAX_TAPS 32
+template <typename TA>
+__global__ void conv_state_update_kernel(const TA* __restrict__ x, int ld, int K, float* __restrict__ state,
+                                         long long state_stride, int conv_off, const int* __restrict__ cu_q,
+                                         const int* __restrict__ seg_slot, int C) {
+    const int seg = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int t0 = cu_q[seg], t1 = cu_q[seg + 1], L = t1 - t0;
+    float* cs = state + (long long)seg_slot[seg] * state_stride + conv_off + (size_t)c * (K - 1);
+    float keep[CONV_MAX_TAPS];
+    for (int m = 0; m < K - 1; ++m) {
+        const int back = K - 2 - m;                       // tokens before the segment's last one
+        keep[m] = back < L ? to_f32(x[(size_t)(t1 - 1 - back) * ld + c]) : cs[K - 2 - (back - L)];
+    }
+    for (int m = 0; m < K - 1; ++m) cs[m] = keep[m];
+}
+
+RB_EXPORT int rb_conv_state_update(const void* x, int ld, int K, float* state, long long state_stride, int conv_off,
+                                   const int* cu_q, const int* seg_slot, int act_dtype, int C, int segments,
+                                   cudaStream_t st) {
+    if (segments <= 0 || K <= 1) return 0;
+    if (K - 1 > CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
+    dim3 grid((C + 127) / 128, segments);
+    if (act_dtype == RB_F32)
+        conv_state_update_kernel<float><<<grid, 128, 0, st>>>((const float*)x, ld, K, state, state_stride, conv_off, cu_q, seg_slot, C);
+    else
+        conv_state_update_kernel<bf16><<<grid, 128, 0, st>>>((const bf16*)x, ld, K, state, state_stride, conv_off, cu_q, seg_slot, C);
+    return rb_launch_status();
+}
+
+// ---------------------------------------------------------------- after the scan: per-head norm, weight, gate
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w * act(gate[t, h, :]), one warp a (token, head).
+// w_mode 0: no weight; 1: a weight of size V shared by the heads; 2: a weight over all heads (H*V).
+// gate_act 0: silu, 1: sigmoid.  The gate has the activation type and rows of stride gate_ld.
+template <typename TA>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const TA* __restrict__ gate, int gate_ld,
+                                      const void* __restrict__ w, int w_dtype, int w_mode, int gate_act, float eps,
+                                      TA* __restrict__ out, int rows, int H, int V) {
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int t = row / H, h = row - t * H;
+    const float* x = o + (size_t)row * V;
+    float ss = 0.f;
+    for (int i = lane; i < V; i += 32) ss = fmaf(x[i], x[i], ss);
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss / (float)V + eps);
+    const TA* g = gate + (size_t)t * gate_ld + (size_t)h * V;
+    TA* y = out + (size_t)row * V;
+    for (int i = lane; i < V; i += 32) {
+        float val = x[i] * rstd;
+        if (w_mode == 1) val *= load_as_f32(w, w_dtype, i);
+        else if (w_mode == 2) val *= load_as_f32(w, w_dtype, (size_t)h * V + i);
+        const float gv = to_f32(g[i]);
+        val *= gate_act == 0 ? gv / (1.0f + expf(-gv)) : 1.0f / (1.0f + expf(-gv));
+        y[i] = from_f32<TA>(val);
+    }
+}
+
+RB_EXPORT int rb_head_norm_gate(const float* o, const void* gate, int gate_ld, const void* w, int w_dtype, int w_mode,
+                                int gate_act, float eps, void* out, int act_dtype, int T, int H, int V, cudaStream_t st) {
+    const int rows = T * H;
+    if (rows <= 0) return 0;
+    const int blocks = (rows + 3) / 4;
+    if (act_dtype == RB_F32)
+        head_norm_gate_kernel<float><<<blocks, 128, 0, st>>>(o, (const float*)gate, gate_ld, w, w_dtype, w_mode, gate_act, eps,
+                                                            (float*)out, rows, H, V);
+    else
+        head_norm_gate_kernel<bf16><<<blocks, 128, 0, st>>>(o, (const bf16*)gate, gate_ld, w, w_dtype, w_mode, gate_act, eps,
+                                                           (bf16*)out, rows, H, V);
+    return rb_launch_status();
+}
+
+// ---------------------------------------------------------------- residual add and one or two norms of the same row
+// stream[t] += s1 * d1[t] + s2 * d2[t] (each delta may be absent; float32 or the activation type), then
+// out1 = stream * rstd * (offset + w1) and, if asked for, out2 = stream * rstd * (offset + w2): the two norms of a
+// block whose mixer and feed-forward read the same stream share the row's mean square.  Without out1 only the add
+// is done.  With `rows` only the listed rows are normed and the stream is left as it is.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+add_dual_norm_kernel(float* __restrict__ stream, const void* __restrict__ d1, int d1_f32, float s1,
+                     const void* __restrict__ d2, int d2_f32, float s2, const int* __restrict__ rows,
+                     const void* __restrict__ w1, const void* __restrict__ w2, int w_dtype, float eps, float offset,
+                     TA* __restrict__ out1, TA* __restrict__ out2, int H) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t t = rows ? (size_t)rows[r] : (size_t)r;
+    float* xr = stream + t * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = xr[i];
+        if (d1 || d2) {
+            float d = 0.f;
+            if (d1) d = s1 * ld_elem(d1, d1_f32, t * H + i);
+            if (d2) d = fmaf(s2, ld_elem(d2, d2_f32, t * H + i), d);
+            v += d;
+            if (!rows) xr[i] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    if (!out1) return;
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = xr[i];
+        if (rows && (d1 || d2)) {                      // the stream was not written: add again
+            float d = 0.f;
+            if (d1) d = s1 * ld_elem(d1, d1_f32, t * H + i);
+            if (d2) d = fmaf(s2, ld_elem(d2, d2_f32, t * H + i), d);
+            v += d;
+        }
+        v *= rstd;
+        out1[(size_t)r * H + i] = from_f32<TA>(v * (offset + load_as_f32(w1, w_dtype, i)));
+        if (out2) out2[(size_t)r * H + i] = from_f32<TA>(v * (offset + load_as_f32(w2, w_dtype, i)));
+    }
+}
+
+RB_EXPORT int rb_add_dual_norm(float* stream, const void* d1, int d1_f32, float s1, const void* d2, int d2_f32, float s2,
+                               const int* rows, const void* w1, const void* w2, int w_dtype, float eps, float offset,
+                               void* out1, void* out2, int act_dtype, int n, int H, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (act_dtype == RB_F32)
+        add_dual_norm_kernel<float><<<n, 256, 0, st>>>(stream, d1, d1_f32, s1, d2, d2_f32, s2, rows, w1, w2, w_dtype, eps,
+                                                      offset, (float*)out1, (float*)out2, H);
+    else
+        add_dual_norm_kernel<bf16><<<n, 256, 0, st>>>(stream, d1, d1_f32, s1, d2, d2_f32, s2, rows, w1, w2, w_dtype, eps,
+                                                     offset, (bf16*)out1, (bf16*)out2, H);
+    return rb_launch_status();
+}
+
+// ---------------------------------------------------------------- y = s1 * a + s2 * b, elementwise (sum of two mixers)
+template <typename TO>
+__global__ void scaled_sum_kernel(const void* __restrict__ a, int a_f32, float s1, const void* __restrict__ b, int b_f32,
+                                  float s2, TO* __restrict__ y, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = from_f32<TO>(fmaf(s2, ld_elem(b, b_f32, i), s1 * ld_elem(a, a_f32, i)));
+}
+
+RB_EXPORT int rb_scaled_sum(const void* a, int a_f32, float s1, const void* b, int b_f32, float s2, void* y, int out_f32,
+                            long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    if (out_f32) scaled_sum_kernel<float><<<blocks, 256, 0, st>>>(a, a_f32, s1, b, b_f32, s2, (float*)y, (size_t)n);
+    else scaled_sum_kernel<bf16><<<blocks, 256, 0, st>>>(a, a_f32, s1, b, b_f32, s2, (bf16*)y, (size_t)n);
+    return rb_launch_status();
+}

@@ -108,6 +108,7 @@ def build_all():
     """Compiles every library of the package (nvcc cross-compiles, no GPU needed); returns the paths."""
     paths = [build.library_path("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})]
     paths.append(build.library_path("return_tc5", _TC5_SOURCES, _tc5_defines()))
+    paths.append(build.library_path("return_recurrent", _RECURRENT_SOURCES, {"RB_PDL_MODE": PDL_MODE}))
     for d in TC5_ATTENTION_HEAD_DIMS:
         paths.append(build.library_path(f"return_attn_tc5_d{d}", ["attention_tc5.cu"], _attn_tc5_defines(d)))
     for d in PREBUILT_HEAD_DIMS:
@@ -743,6 +744,154 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
         attention_decode_mma(qkv, k_pool, v_pool, batch.decode_segs, batch.cu_q, batch.seg_kv_len, block_table,
                              page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
                              _decode_split_count(batch, num_heads, num_kv_heads, window), getattr(batch, "scratch", None))
+
+
+# ------------------------------------------------------------------------------- mixers with a matrix state
+
+_recurrent = None
+_RECURRENT_SOURCES = ["recurrent.cu"]
+SCAN_DECAY, SCAN_MEMORY, SCAN_DELTA = 0, 1, 2
+SCAN_MAX_KEY_DIM = 256
+
+
+def recurrent_lib() -> ctypes.CDLL:
+    """The kernels of the mixers that keep a matrix state per head (csrc/recurrent.cu); compiled when a model
+    that has such a mixer is first run."""
+    global _recurrent
+    if _recurrent is None:
+        lib = build.load("return_recurrent", _RECURRENT_SOURCES, {"RB_PDL_MODE": PDL_MODE})
+        P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
+        lib.rb_linear_scan.argtypes = [I, P, P, P, I, I, I, I, I, I, P, P, F, F, P, L, I, I, I, P, P, P, I, I, I, I, I, P]
+        lib.rb_rotary_to_f32.argtypes = [P, I, I, I, P, P, I, P, P, P, I, I, I, I, F, F, P]
+        lib.rb_delta_prep.argtypes = [P, I, P, I, I, P, L, I, P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, P]
+        lib.rb_conv_state_update.argtypes = [P, I, I, P, L, I, P, P, I, I, I, P]
+        lib.rb_head_norm_gate.argtypes = [P, P, I, P, I, I, I, F, P, I, I, I, I, P]
+        lib.rb_add_dual_norm.argtypes = [P, P, I, F, P, I, F, P, P, P, I, F, F, P, P, I, I, I, P]
+        lib.rb_scaled_sum.argtypes = [P, I, F, P, I, F, P, I, L, P]
+        for name in ("rb_linear_scan", "rb_rotary_to_f32", "rb_delta_prep", "rb_conv_state_update",
+                     "rb_head_norm_gate", "rb_add_dual_norm", "rb_scaled_sum"):
+            getattr(lib, name).restype = c_int
+        _recurrent = lib
+    return _recurrent
+
+
+def _is_f32(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 1
+    if t.dtype == torch.bfloat16:
+        return 0
+    raise KernelError(f"the kernels take float32 and bfloat16, not {t.dtype}")
+
+
+def linear_scan(mode: int, q, k, v, gate_a, gate_b, state, offsets, batch, out, heads: int, kv_heads: int,
+                dim: int, vdim: int, q_scale: float = 1.0, cap: float = 0.0) -> None:
+    """The recurrence of a mixer with a [dim, vdim] state per head, over every segment of the step, token by token.
+
+    q, k: [T, >= kv_heads * dim] views (float32 or bfloat16, unit stride along a row), v: [T, >= heads * vdim];
+    ``state``: float32 [slots, n], the row of a segment is ``batch.seg_slot``; ``offsets`` = (S, n, m): where the
+    matrix, the normaliser and the running maximum start inside a row (the last two for ``SCAN_MEMORY`` only).
+    ``gate_a`` / ``gate_b`` by mode: SCAN_DECAY: [heads] decays / None; SCAN_MEMORY: [T, 2 heads] gate
+    pre-activations (input, forget) / [2 heads] biases; SCAN_DELTA: [T, heads, dim] row decays / [T, heads] beta.
+    out: float32 [T, heads * vdim]."""
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == heads * vdim
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and dim <= SCAN_MAX_KEY_DIM
+    assert gate_a.dtype == torch.float32 and gate_a.is_contiguous()
+    if gate_b is not None:
+        assert gate_b.dtype == torch.float32 and gate_b.is_contiguous()
+    _check(recurrent_lib().rb_linear_scan(
+        mode, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _is_f32(q), _is_f32(k), _is_f32(v),
+        _ptr(gate_a), _ptr(gate_b), cap, q_scale, _ptr(state), state.stride(0), offsets[0], offsets[1], offsets[2],
+        _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(out), heads, kv_heads, dim, vdim, batch.num_segments, _stream()),
+        "linear_scan")
+
+
+def rotary_to_f32(x, q_off: int, k_off: int, cos, sin, rot: int, pos, q32, k32, heads: int, dim: int,
+                  q_scale: float = 1.0, k_scale: float = 1.0) -> None:
+    """q and k heads of the projection rows ``x`` (q at column q_off, k at k_off), turned by their positions on the
+    first ``rot`` elements (element i with i + rot/2) and scaled, into float32 q32, k32 [T, heads * dim]."""
+    T = x.shape[0]
+    assert x.stride(1) == 1 and q32.dtype == k32.dtype == torch.float32 and q32.is_contiguous() and k32.is_contiguous()
+    if rot:
+        assert cos.dtype == sin.dtype == torch.float32 and cos.shape[1] * 2 == rot and cos.is_contiguous() and sin.is_contiguous()
+    else:
+        cos = sin = q32
+    _check(recurrent_lib().rb_rotary_to_f32(_ptr(x), x.stride(0), q_off, k_off, _ptr(cos), _ptr(sin), rot, _ptr(pos),
+                                            _ptr(q32), _ptr(k32), dtype_code(x.dtype), T, heads, dim, q_scale, k_scale,
+                                            _stream()), "rotary_to_f32")
+
+
+def delta_prep(x, taps, state, conv_off: int, batch, q32, k32, v32, a, A_log, dt_bias, b, heads: int, kv_heads: int,
+               dim: int, vdim: int, q_scale: float) -> None:
+    """What the delta rule needs of every token: the short causal convolution and silu of the q, k, v channels of
+    ``x`` (what lies before a segment comes from the request's conv state), unit q and k heads, the row decays (in
+    place over ``a``) and beta (in place over ``b``)."""
+    T = x.shape[0]
+    K = taps.shape[1]
+    assert x.stride(1) == 1 and taps.is_contiguous() and taps.shape[0] == 2 * kv_heads * dim + heads * vdim
+    assert a.dtype == b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous()
+    assert A_log.dtype == dt_bias.dtype
+    for t in (q32, k32, v32):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    _check(recurrent_lib().rb_delta_prep(
+        _ptr(x), x.stride(0), _ptr(taps), dtype_code(taps.dtype), K, _ptr(state), state.stride(0), conv_off,
+        _ptr(batch.tok_seg), _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(q32), _ptr(k32), _ptr(v32), _ptr(a),
+        _ptr(A_log), _ptr(dt_bias), dtype_code(A_log.dtype), _ptr(b), dtype_code(x.dtype), T, heads, kv_heads, dim, vdim,
+        q_scale, _stream()), "delta_prep")
+
+
+def conv_state_update(x, taps_count: int, state, conv_off: int, batch, channels: int) -> None:
+    """The conv state of every segment's request after this step: the last ``taps_count - 1`` inputs of each of the
+    first ``channels`` columns of ``x``."""
+    _check(recurrent_lib().rb_conv_state_update(_ptr(x), x.stride(0), taps_count, _ptr(state), state.stride(0), conv_off,
+                                                _ptr(batch.cu_q), _ptr(batch.seg_slot), dtype_code(x.dtype), channels,
+                                                batch.num_segments, _stream()), "conv_state_update")
+
+
+def head_norm_gate(o, gate, weight, weight_mode: int, gate_act: int, eps: float, out, heads: int, vdim: int) -> None:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * act(gate[t, h]).  o float32 [T, heads * vdim]; gate: a view
+    [T, heads * vdim] of the activation type.  weight_mode 0: none, 1: [vdim] shared by the heads, 2: [heads * vdim].
+    gate_act 0: silu, 1: sigmoid."""
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and gate.stride(1) == 1
+    assert gate.dtype == out.dtype
+    wd = dtype_code(weight.dtype) if weight is not None else F32
+    _check(recurrent_lib().rb_head_norm_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), wd, weight_mode, gate_act,
+                                             eps, _ptr(out), dtype_code(out.dtype), T, heads, vdim, _stream()),
+           "head_norm_gate")
+
+
+def add_dual_norm(stream, deltas, w1, w2, eps: float, offset: float, out1, out2, rows=None) -> None:
+    """stream (float32) += the deltas (up to two tensors of the stream's shape, float32 or bfloat16; written back
+    unless ``rows``), then out1 = norm(stream) * (offset + w1) and, if given, out2 likewise with w2: two norms of the
+    same row share its mean square.  out1 None: the add only.  ``rows`` (int32): only these rows are normed."""
+    H = stream.shape[1]
+    assert stream.dtype == torch.float32 and stream.is_contiguous()
+    ds = [d for d in (deltas or ()) if d is not None]
+    assert len(ds) <= 2
+    for d in ds:
+        assert d.shape == stream.shape and d.is_contiguous()
+    d1 = ds[0] if ds else None
+    d2 = ds[1] if len(ds) > 1 else None
+    n = stream.shape[0] if rows is None else rows.numel()
+    if out1 is not None:
+        assert out1.is_contiguous() and out1.shape == (n, H) and w1.numel() == H
+        if out2 is not None:
+            assert out2.dtype == out1.dtype and out2.shape == out1.shape and w2.dtype == w1.dtype and out2.is_contiguous()
+    elif not ds:
+        return
+    _check(recurrent_lib().rb_add_dual_norm(
+        _ptr(stream), _ptr(d1), _is_f32(d1) if d1 is not None else 1, 1.0, _ptr(d2), _is_f32(d2) if d2 is not None else 1,
+        1.0, _ptr(rows), _ptr(w1), _ptr(w2), dtype_code(w1.dtype) if w1 is not None else F32, eps, offset, _ptr(out1),
+        _ptr(out2), dtype_code(out1.dtype) if out1 is not None else F32, n, H, _stream()), "add_dual_norm")
+
+
+def scaled_sum(a, s1: float, b, s2: float, out) -> None:
+    """out = s1 * a + s2 * b, elementwise; each of a, b and out float32 or bfloat16."""
+    assert a.shape == b.shape == out.shape
+    assert a.is_contiguous() and b.is_contiguous() and out.is_contiguous()
+    _check(recurrent_lib().rb_scaled_sum(_ptr(a), _is_f32(a), s1, _ptr(b), _is_f32(b), s2, _ptr(out), _is_f32(out),
+                                         a.numel(), _stream()), "scaled_sum")
 
 
 # ------------------------------------------------------------------------------- sampling

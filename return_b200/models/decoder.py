@@ -26,6 +26,7 @@ class DecoderModel:
         self.env = env
         self.blocks = [BLOCKS.build(b, env) for b in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, env)
+        self.embedding_norm = NORMS.build(spec.embedding_norm, env) if spec.embedding_norm is not None else None
         self.embed: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
 
@@ -38,6 +39,9 @@ class DecoderModel:
                 p[f"layers.{i}.{name}"] = ps
         for name, ps in self.final_norm.params().items():
             p[f"final_norm.{name}"] = ps
+        if self.embedding_norm is not None:
+            for name, ps in self.embedding_norm.params().items():
+                p[f"embedding_norm.{name}"] = ps
         if not s.tie_embeddings:
             p["lm_head"] = ParamSpec((s.vocab_size, s.hidden_size))
         return p
@@ -49,6 +53,9 @@ class DecoderModel:
             prefix = f"layers.{i}."
             block.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
         self.final_norm.bind({k[len("final_norm."):]: v for k, v in tensors.items() if k.startswith("final_norm.")})
+        if self.embedding_norm is not None:
+            self.embedding_norm.bind({k[len("embedding_norm."):]: v for k, v in tensors.items()
+                                      if k.startswith("embedding_norm.")})
 
     @property
     def graph_safe(self) -> bool:
@@ -80,6 +87,13 @@ class DecoderModel:
             out.append(self.blocks[e.layer].cache_need() if e.cache_of is None else None)
         return out
 
+    @staticmethod
+    def _fold(stream, deltas):
+        """A block may leave several outputs still to be added to the stream (one per branch); whoever cannot take
+        them as they are gets them added here."""
+        ops.add_dual_norm(stream, deltas, None, None, 0.0, 0.0, None, None)
+        return None
+
     # ------------------------------------------------------------------ one step
     def forward(self, batch, storage) -> torch.Tensor:
         """Runs the step's tokens through the schedule; returns float32 logits [n_want, vocab]."""
@@ -88,6 +102,8 @@ class DecoderModel:
         dev = self.env.device
         stream = torch.empty((T, H), dtype=torch.float32, device=dev)
         ops.embedding(self.embed, batch.tokens, stream)
+        if self.embedding_norm is not None:
+            self.embedding_norm.forward(stream, stream)           # in place: a warp reads its row before it writes it
         delta = None
         schedule = self.spec.schedule
         for index, entry in enumerate(schedule):
@@ -95,7 +111,12 @@ class DecoderModel:
             ctx = storage.layer_context(owner, batch, write=entry.cache_of is None)
             ctx.position = index
             ctx.next_block = self.blocks[schedule[index + 1].layer] if index + 1 < len(schedule) else None
-            delta = self.blocks[entry.layer].forward(stream, delta, ctx)
+            block = self.blocks[entry.layer]
+            if isinstance(delta, tuple) and not getattr(block, "takes_delta_pair", False):
+                delta = self._fold(stream, delta)
+            delta = block.forward(stream, delta, ctx)
+        if isinstance(delta, tuple):
+            delta = self._fold(stream, delta)
         n_want = batch.num_want
         logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=dev)
         if n_want:

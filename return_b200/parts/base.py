@@ -55,6 +55,13 @@ class StateNeed:
 
 
 @dataclass(frozen=True)
+class CompositeNeed:
+    """The mixer is made of named children with cache needs of their own (None for a child that has none).  Its
+    run then finds a context per child under ``ctx.children[name]``."""
+    children: Tuple[Tuple[str, Any], ...]
+
+
+@dataclass(frozen=True)
 class Tiling:
     """A table a part wants in every step's batch: the step's segments of several tokens cut into blocks of
     ``rows`` query rows, as (segment, first row within it) pairs.  ``heaviest_first``: the blocks with the most
@@ -82,6 +89,7 @@ class LayerContext:
     position: int = -1                        # index of this run in the model's schedule
     next_block: Any = None                    # the block that runs after this one in this step, or None (a block may
                                               # prepare what its successor's first norm needs)
+    children: Optional[Dict[str, "LayerContext"]] = None   # per child of a mixer with a CompositeNeed
 
     def buffer(self, name: str, shape, dtype, device) -> torch.Tensor:
         """An uninitialised work buffer for the part that asks.  The layers of a step run one after the

@@ -129,3 +129,71 @@ class PreNormBlock(Block):
         mixed = self.mixer.forward(a, ctx)
         self.feed_forward_norm.add_forward(stream, mixed, a)      # stream += mixed; a = norm(stream)
         return self.feed_forward.forward(a, ctx)
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock(Block):
+    """x += mixer(norm_a(x)) + feed_forward(norm_b(x)): both branches read the same stream.
+
+    The two norms are one kernel (they share the row's mean square), fused with the adds that the block before left
+    undone: a block of this kind returns its two branch outputs as a pair, and whoever runs next adds them
+    (``takes_delta_pair``: this kind does it inside its norm kernel; for any other the model adds them first)."""
+
+    takes_delta_pair = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.mixer = MIXERS.build(spec.mixer, env)
+        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, env) if spec.feed_forward is not None else None
+        self.mixer_norm = NORMS.build(spec.mixer_norm, env)
+        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, env) if spec.feed_forward is not None else None
+        na, nb = spec.mixer_norm, spec.feed_forward_norm
+        if getattr(na, "kind", None) != "rmsnorm" or (nb is not None and (getattr(nb, "kind", None) != "rmsnorm" or
+                                                                           (nb.eps, nb.offset, nb.size) != (na.eps, na.offset, na.size))):
+            raise ValueError("the two norms of a parallel block are RMSNorms with the same eps, offset and size")
+        self._children = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.feed_forward is not None:
+            self._children.update({"feed_forward": self.feed_forward, "feed_forward_norm": self.feed_forward_norm})
+
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part in self._children.values())
+
+    def params(self):
+        return {f"{child}.{name}": p for child, part in self._children.items()
+                for name, p in part.params().items()}
+
+    def bind(self, tensors):
+        for child, part in self._children.items():
+            prefix = child + "."
+            part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def batch_tilings(self):
+        out = {}
+        for part in self._children.values():
+            out.update(part.batch_tilings())
+        return out
+
+    def graph_variant(self, n_tokens, longest_context):
+        out = {}
+        for part in self._children.values():
+            out.update(part.graph_variant(n_tokens, longest_context))
+        return out
+
+    def forward(self, stream, delta, ctx):
+        T, H = stream.shape
+        dt, dev = self.env.act_dtype, stream.device
+        n = self.mixer_norm.spec
+        deltas = delta if isinstance(delta, tuple) else (delta,)
+        a = ctx.buffer("parallel.normed_a", (T, H), dt, dev)
+        has_ff = self.feed_forward is not None
+        b = ctx.buffer("parallel.normed_b", (T, H), dt, dev) if has_ff else None
+        ops.add_dual_norm(stream, deltas, self.mixer_norm.p_weight, self.feed_forward_norm.p_weight if has_ff else None,
+                          n.eps, n.offset, a, b)
+        mixed = self.mixer.forward(a, ctx)
+        if not has_ff:
+            return (mixed,)
+        return (mixed, self.feed_forward.forward(b, ctx))

@@ -1,0 +1,182 @@
+"""Mixers that keep a matrix state per head and request instead of cached keys: retention (a fixed decay a
+head), the gated delta rule with a decay per key channel, and the matrix memory with exponential gates.
+
+All three are "product, recurrence, product": the input projections are one matrix product (their weights
+concatenated at load), the recurrence runs in float32 whatever the activation type (``csrc/recurrent.cu``: one
+kernel walks every segment of the step token by token, so prompts, portions and single tokens are one path and a
+token's result does not depend on the cutting), the read-out is normed per head, gated and projected out.
+
+A request's state is one float32 row of its slot (``StateNeed``): the matrices S [heads, key rows in groups of 8,
+value dim, 8] first, then what else the mixer carries (conv inputs; normaliser and running maximum).  A slot is
+zeroed when a request takes it, which is every part's starting state.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ext import ops
+from .base import MIXERS, POSITION_ENCODINGS, Mixer, ParamSpec, StateNeed
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+class _StateMixer(Mixer):
+    """What the three share: sizes, the state row's layout, buffers."""
+
+    def _sizes(self):
+        s = self.spec
+        self.H, self.D, self.V = s.num_heads, s.key_dim, s.value_dim
+        if self.D > ops.SCAN_MAX_KEY_DIM:
+            raise ValueError(f"key_dim={self.D}: the scan kernel holds up to {ops.SCAN_MAX_KEY_DIM} key rows a head")
+        self.s_floats = self.H * _pad8(self.D) * self.V
+
+    def out_projection(self):
+        return self.p_o
+
+    def _project_out(self, mixed, ctx):
+        y = ctx.buffer(self.spec.kind + ".y", (mixed.shape[0], self.spec.hidden_size), torch.float32, mixed.device)
+        ops.linear(mixed, self.p_o, y)
+        return y
+
+
+@MIXERS.register("retention")
+class Retention(_StateMixer):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self._sizes()
+        if len(spec.decay) != spec.num_heads:
+            raise ValueError(f"{len(spec.decay)} decays for {spec.num_heads} heads")
+        self.position = POSITION_ENCODINGS.build(spec.position, env) if spec.position is not None else None
+        if self.position is not None and self.position.rotary_tables is None:
+            raise ValueError("retention rotates pairs of a head: the position encoding must give rotary tables")
+        self._decay = None
+
+    def params(self):
+        s = self.spec
+        return {"in": ParamSpec((2 * self.H * self.D + 2 * self.H * self.V, s.hidden_size)),
+                "o": ParamSpec((s.hidden_size, self.H * self.V))}
+
+    def cache_need(self):
+        return StateNeed((self.s_floats,), torch.float32)
+
+    def forward(self, x, ctx):
+        s, b = self.spec, ctx.batch
+        T, dev = x.shape[0], x.device
+        HD, HV = self.H * self.D, self.H * self.V
+        proj = ctx.buffer("retention.in", (T, 2 * HD + 2 * HV), x.dtype, dev)
+        ops.linear(x, self.p_in, proj)
+        q32 = ctx.buffer("retention.q", (T, HD), torch.float32, dev)
+        k32 = ctx.buffer("retention.k", (T, HD), torch.float32, dev)
+        cos, sin, rot = self.position.rotary_tables() if self.position is not None else (None, None, 0)
+        ops.rotary_to_f32(proj, 0, HD, cos, sin, rot, b.pos, q32, k32, self.H, self.D, 1.0, self.D ** -0.5)
+        if self._decay is None:
+            self._decay = torch.tensor(s.decay, dtype=torch.float32, device=dev)
+        o = ctx.buffer("retention.o", (T, HV), torch.float32, dev)
+        ops.linear_scan(ops.SCAN_DECAY, q32, k32, proj[:, 2 * HD:2 * HD + HV], self._decay, None, ctx.state,
+                        (0, 0, 0), b, o, self.H, self.H, self.D, self.V)
+        mixed = ctx.buffer("retention.mixed", (T, HV), x.dtype, dev)
+        ops.head_norm_gate(o, proj[:, 2 * HD + HV:], None, 0, 0, s.eps, mixed, self.H, self.V)
+        return self._project_out(mixed, ctx)
+
+
+@MIXERS.register("channel_delta")
+class ChannelDelta(_StateMixer):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self._sizes()
+        s = spec
+        if s.num_heads % s.num_kv_heads:
+            raise ValueError(f"num_heads={s.num_heads} is not a multiple of num_kv_heads={s.num_kv_heads}")
+        if not (1 <= s.conv_taps <= 33):
+            raise ValueError("conv_taps: 1 to 33")
+        if s.unit_eps != 1e-6:
+            raise ValueError("the kernel's unit vectors use 1e-6 under the root")
+        self.G = s.num_kv_heads
+        self.channels = 2 * self.G * self.D + self.H * self.V
+        self.conv_off = self.s_floats
+
+    def params(self):
+        s = self.spec
+        C, HD, HV = self.channels, self.H * self.D, self.H * self.V
+        return {"in": ParamSpec((C + s.decay_rank + s.gate_rank, s.hidden_size)),          # q, k, v, decay low rank, gate low rank
+                "conv": ParamSpec((C, s.conv_taps), role="vector", init="normal:0.5"),
+                "beta": ParamSpec((self.H, s.hidden_size)),
+                "decay_up": ParamSpec((HD, s.decay_rank), init="normal:0.2"),
+                "gate_up": ParamSpec((HV, s.gate_rank), init="normal:0.2"),
+                "A_log": ParamSpec((self.H,), role="vector", init="normal:0.5"),
+                "dt_bias": ParamSpec((HD,), role="vector", init="normal:0.5"),
+                "norm": ParamSpec((self.V,), role="vector", init="ones_normal"),
+                "o": ParamSpec((s.hidden_size, HV))}
+
+    def cache_need(self):
+        return StateNeed((self.s_floats + self.channels * (self.spec.conv_taps - 1),), torch.float32)
+
+    def forward(self, x, ctx):
+        s, b = self.spec, ctx.batch
+        T, dev = x.shape[0], x.device
+        C, GD, HD, HV = self.channels, self.G * self.D, self.H * self.D, self.H * self.V
+        proj = ctx.buffer("channel_delta.in", (T, C + s.decay_rank + s.gate_rank), x.dtype, dev)
+        ops.linear(x, self.p_in, proj)
+        beta = ctx.buffer("channel_delta.beta", (T, self.H), torch.float32, dev)
+        ops.linear(x, self.p_beta, beta)
+        decay = ctx.buffer("channel_delta.decay", (T, HD), torch.float32, dev)
+        ops.linear(proj[:, C:C + s.decay_rank], self.p_decay_up, decay)
+        gate = ctx.buffer("channel_delta.gate", (T, HV), x.dtype, dev)
+        ops.linear(proj[:, C + s.decay_rank:], self.p_gate_up, gate)
+        q32 = ctx.buffer("channel_delta.q", (T, GD), torch.float32, dev)
+        k32 = ctx.buffer("channel_delta.k", (T, GD), torch.float32, dev)
+        v32 = ctx.buffer("channel_delta.v", (T, HV), torch.float32, dev)
+        ops.delta_prep(proj, self.p_conv, ctx.state, self.conv_off, b, q32, k32, v32, decay, self.p_A_log,
+                       self.p_dt_bias, beta, self.H, self.G, self.D, self.V, self.D ** -0.5)
+        ops.conv_state_update(proj, s.conv_taps, ctx.state, self.conv_off, b, C)      # after every token read the old one
+        o = ctx.buffer("channel_delta.o", (T, HV), torch.float32, dev)
+        ops.linear_scan(ops.SCAN_DELTA, q32, k32, v32, decay, beta, ctx.state, (0, 0, 0), b, o,
+                        self.H, self.G, self.D, self.V)
+        mixed = ctx.buffer("channel_delta.mixed", (T, HV), x.dtype, dev)
+        ops.head_norm_gate(o, gate, self.p_norm, 1, 1, s.eps, mixed, self.H, self.V)
+        return self._project_out(mixed, ctx)
+
+
+@MIXERS.register("matrix_memory")
+class MatrixMemory(_StateMixer):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self._sizes()
+        if spec.gate_cap <= 0:
+            raise ValueError("gate_cap must be positive")
+        self.n_off = self.s_floats
+        self.m_off = self.n_off + self.H * _pad8(self.D)
+
+    def params(self):
+        s = self.spec
+        HD, HV = self.H * self.D, self.H * self.V
+        return {"in": ParamSpec((2 * HD + 2 * HV, s.hidden_size)),                       # q, k, v, output gate
+                "gates": ParamSpec((2 * self.H, s.hidden_size)),                         # input gate rows, forget gate rows
+                "gate_bias": ParamSpec((2 * self.H,), role="vector", init="normal:0.5"),
+                "norm": ParamSpec((HV,), role="vector", init="ones_normal"),
+                "o": ParamSpec((s.hidden_size, HV))}
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self._bias32 = self.p_gate_bias.float().contiguous()
+
+    def cache_need(self):
+        return StateNeed((self.m_off + self.H,), torch.float32)
+
+    def forward(self, x, ctx):
+        s, b = self.spec, ctx.batch
+        T, dev = x.shape[0], x.device
+        HD, HV = self.H * self.D, self.H * self.V
+        proj = ctx.buffer("matrix_memory.in", (T, 2 * HD + 2 * HV), x.dtype, dev)
+        ops.linear(x, self.p_in, proj)
+        gates = ctx.buffer("matrix_memory.gates", (T, 2 * self.H), torch.float32, dev)
+        ops.linear(x, self.p_gates, gates)
+        o = ctx.buffer("matrix_memory.o", (T, HV), torch.float32, dev)
+        ops.linear_scan(ops.SCAN_MEMORY, proj[:, :HD], proj[:, HD:2 * HD], proj[:, 2 * HD:2 * HD + HV], gates,
+                        self._bias32, ctx.state, (0, self.n_off, self.m_off), b, o, self.H, self.H, self.D, self.V,
+                        q_scale=self.D ** -0.5, cap=s.gate_cap)
+        mixed = ctx.buffer("matrix_memory.mixed", (T, HV), x.dtype, dev)
+        ops.head_norm_gate(o, proj[:, 2 * HD + HV:], self.p_norm, 2, 1, s.eps, mixed, self.H, self.V)
+        return self._project_out(mixed, ctx)

@@ -8,6 +8,8 @@ kernel that writes the cache (csrc/rope_cache.cu).
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import POSITION_ENCODINGS, PositionEncoding
@@ -37,6 +39,43 @@ class RotaryEncoding(PositionEncoding):
                 ang = torch.outer(torch.arange(s.max_positions, dtype=torch.float32), inv_freq)
                 shared = _TABLES[key] = (ang.cos().contiguous().to(self.env.device),
                                          ang.sin().contiguous().to(self.env.device), s.rotary_dim)
+            self._tables = shared
+        return self._tables
+
+
+@POSITION_ENCODINGS.register("rope_scaled")
+class ScaledRotaryEncoding(PositionEncoding):
+    """Rotary tables with optional slowing of the long wavelengths (``ScaledRopeSpec``).  Frequencies and angles are
+    worked out in float64 on the host and rounded once, to the float32 tables the kernels read."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.rotary_dim % 2:
+            raise ValueError(f"rotary_dim={spec.rotary_dim} must be even")
+        self._tables = None
+
+    @staticmethod
+    def frequencies(rotary_dim: int, theta: float, scaling=None) -> torch.Tensor:
+        half = rotary_dim // 2
+        f = float(theta) ** (-torch.arange(0, half, dtype=torch.float64) / half)
+        if scaling is not None:
+            factor, low, high, original = (float(v) for v in scaling)
+            wavelength = 2.0 * math.pi / f
+            blend = ((original / wavelength - low) / (high - low)).clamp(0.0, 1.0)
+            mixed = (1.0 - blend) * f / factor + blend * f
+            f = torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, mixed))
+        return f
+
+    def rotary_tables(self):
+        if self._tables is None:
+            s = self.spec
+            key = ("scaled", s.rotary_dim, float(s.theta), s.scaling, s.max_positions, str(self.env.device))
+            shared = _TABLES.get(key)
+            if shared is None:
+                f = self.frequencies(s.rotary_dim, s.theta, s.scaling)
+                ang = torch.outer(torch.arange(s.max_positions, dtype=torch.float64), f)
+                shared = _TABLES[key] = (ang.cos().float().contiguous().to(self.env.device),
+                                         ang.sin().float().contiguous().to(self.env.device), s.rotary_dim)
             self._tables = shared
         return self._tables
 

@@ -34,6 +34,19 @@ class RopeSpec:
 
 
 @dataclass(frozen=True)
+class ScaledRopeSpec:
+    """Half-split rotary encoding of the first ``rotary_dim`` elements of a head whose long wavelengths may be slowed
+    down.  ``scaling`` None, or (factor, low, high, original): with wavelength l = 2 pi / f, f is kept where
+    l < original / high, divided by factor where l > original / low, and blended linearly in
+    s = (original / l - low) / (high - low) between the two.  Tables are worked out in float64."""
+    rotary_dim: int
+    theta: float
+    max_positions: int
+    scaling: Optional[Tuple[float, float, float, float]] = None
+    kind: str = "rope_scaled"
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Causal grouped-query attention over a paged cache."""
     hidden_size: int
@@ -45,6 +58,80 @@ class AttentionSpec:
     qk_norm: Optional[NormSpec] = None    # per-head norm of q and k before the rotation
     position: Optional[Any] = None        # a position-encoding spec, e.g. RopeSpec
     kind: str = "attention"
+    # Key and value sizes of the checkpoint's heads where they differ from ``head_dim``: the heads are then padded with
+    # zeros to ``head_dim`` when the weights are loaded (zero key elements add nothing to a score, zero value
+    # elements meet zero columns of the output projection), so one cache layout and one set of kernels serve them.
+    key_dim: Optional[int] = None
+    value_dim: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with one fixed decay a head and no softmax: S <- decay S + k v^T, o = S^T q; q and k are
+    rotated (``position``), k is scaled by key_dim^-1/2; each head's o is divided by its root mean square, gated
+    by silu of a projection of the input, and projected out."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    decay: Tuple[float, ...]
+    eps: float
+    position: Optional[Any] = None
+    kind: str = "retention"
+
+
+@dataclass(frozen=True)
+class ChannelDeltaSpec:
+    """Gated delta rule with a decay per head and key channel.  q, k (``num_kv_heads`` heads) and v pass a causal
+    convolution of ``conv_taps`` taps and silu; q and k become unit vectors (``unit_eps`` under the root), q times
+    key_dim^-1/2; beta = sigmoid of a projection; the decay is exp(-exp(A_log) softplus(low-rank projection +
+    dt_bias)); the read-out is normed per head, weighted, gated by sigmoid of a low-rank projection."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    decay_rank: int
+    gate_rank: int
+    eps: float
+    unit_eps: float = 1e-6
+    kind: str = "channel_delta"
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec:
+    """Matrix memory with exponential input and forget gates, a normaliser and a running maximum that starts at
+    zero; gate pre-activations are capped softly at ``gate_cap`` (cap tanh(x / cap)); q is scaled by key_dim^-1/2;
+    the read-out is normed per head, weighted over all heads, gated by sigmoid of a projection."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    gate_cap: float
+    eps: float
+    kind: str = "matrix_memory"
+
+
+@dataclass(frozen=True)
+class MixerSumSpec:
+    """Several mixers on the same input; the result is the sum of ``scales[i] * mixers[i](x)``.  ``names`` are the
+    children's names in parameter names and cache needs."""
+    names: Tuple[str, ...]
+    mixers: Tuple[Any, ...]
+    scales: Tuple[float, ...]
+    kind: str = "mixer_sum"
+
+
+@dataclass(frozen=True)
+class ParallelBlockSpec:
+    """x += mixer(norm_a(x)) + feed_forward(norm_b(x)), both norms of the same x.  ``feed_forward`` None: the layer
+    has none."""
+    mixer: Any
+    feed_forward: Any
+    mixer_norm: Any
+    feed_forward_norm: Any
+    kind: str = "parallel"
 
 
 @dataclass(frozen=True)
@@ -84,6 +171,7 @@ class DecoderSpec:
     schedule: Tuple[ScheduleEntry, ...]
     final_norm: Any
     tie_embeddings: bool
+    embedding_norm: Any = None            # a norm applied to the embedded tokens before the first layer
 
     @staticmethod
     def in_order(n_layers: int) -> Tuple[ScheduleEntry, ...]:

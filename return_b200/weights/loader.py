@@ -20,7 +20,7 @@ import json
 import math
 import os
 from dataclasses import dataclass
-from typing import Dict, List, Set, Tuple
+from typing import Dict, List, Optional, Set, Tuple
 
 import torch
 
@@ -33,6 +33,27 @@ class Source:
     ``interleave`` = b, woven in blocks of b rows (b rows of the first, b of the second, ...)."""
     names: Tuple[str, ...]
     interleave: int = 0
+    # Heads padded with zeros on the way in.  ``pad_rows``: per name, None or (rows of a head in the file, rows of a
+    # head in the parameter); ``pad_cols``: the same for the columns of every named tensor.
+    pad_rows: Optional[Tuple[Optional[Tuple[int, int]], ...]] = None
+    pad_cols: Optional[Tuple[int, int]] = None
+
+
+def _pad_heads(t: torch.Tensor, rows: Optional[Tuple[int, int]], cols: Optional[Tuple[int, int]]) -> torch.Tensor:
+    """``t`` with every head's rows (and columns) padded with zeros from the file's size to the parameter's."""
+    if rows is not None and rows[0] != rows[1]:
+        src, dst = rows
+        heads = t.shape[0] // src
+        wide = t.new_zeros((heads, dst) + tuple(t.shape[1:]))
+        wide[:, :src] = t.reshape((heads, src) + tuple(t.shape[1:]))
+        t = wide.reshape((heads * dst,) + tuple(t.shape[1:]))
+    if cols is not None and cols[0] != cols[1]:
+        src, dst = cols
+        heads = t.shape[1] // src
+        wide = t.new_zeros((t.shape[0], heads, dst))
+        wide[:, :, :src] = t.reshape(t.shape[0], heads, src)
+        t = wide.reshape(t.shape[0], heads * dst)
+    return t
 
 
 class WeightError(ValueError):
@@ -108,8 +129,9 @@ def load_parameters(params: Dict[str, "ParamSpec"], sources: Dict[str, Source],
                     woven[:, i].copy_(files.tensor(n).view(-1, b, *dst.shape[1:]))
             else:
                 row = 0
-                for n in names:
-                    t = files.tensor(n)
+                src = sources[pname]
+                for j, n in enumerate(names):
+                    t = _pad_heads(files.tensor(n), src.pad_rows[j] if src.pad_rows else None, src.pad_cols)
                     k = t.shape[0] if t.dim() else 1
                     view = dst[row:row + k] if t.dim() else dst
                     view.copy_(t)
@@ -137,6 +159,12 @@ def random_tensor(seed: int, name: str, shape, init: str, dtype: torch.dtype, de
     x = torch.randn(tuple(shape), generator=g, dtype=torch.float32, device=device)
     if init == "ones_normal":
         x.mul_(0.1).add_(1.0)
+    elif init == "zeros_normal":                   # a weight stored around zero
+        x.mul_(0.1)
+    elif init == "fan_in":                         # deviation inputs^-1/2: outputs as large as inputs
+        x.mul_(float(shape[-1]) ** -0.5)
+    elif init.startswith("normal:"):
+        x.mul_(float(init.split(":", 1)[1]))
     else:
         x.mul_(0.02)
     return x.to(dtype)
@@ -166,6 +194,8 @@ def checkpoint_shapes(arch, config) -> Dict[str, Tuple[Tuple[int, ...], str]]:
     architecture's sources.  Fused parameters are split by the architecture's ``split_rows``."""
     from ..models.decoder import DecoderModel
     from ..parts.base import BuildEnv
+    if getattr(arch, "checkpoint_shapes", None) is not None:
+        return dict(arch.checkpoint_shapes(config))
     model = DecoderModel(arch.decoder_spec(config, 8), BuildEnv(torch.float32, torch.device("cpu")))
     params, sources = model.params(), arch.weight_sources(config)
     split = getattr(arch, "split_rows", None)
@@ -196,8 +226,15 @@ def random_parameters(params: Dict[str, "ParamSpec"], sources: Dict[str, Source]
         dt = act_dtype
         dst = torch.empty(spec.shape, dtype=dt, device=device)
         row = 0                       # random numbers have no order to keep: an interleaved layout is filled the same way
-        for n in sources[pname].names:
+        src = sources[pname]
+        for j, n in enumerate(src.names):
             shp, init = shapes[n]
+            if src.pad_rows or src.pad_cols:      # heads padded with zeros: drawn whole, then padded
+                t = _pad_heads(random_tensor(seed, n, shp, init, dt, device), src.pad_rows[j] if src.pad_rows else None,
+                               src.pad_cols)
+                dst[row:row + t.shape[0]].copy_(t)
+                row += t.shape[0]
+                continue
             k = shp[0]
             # large matrices are drawn in slabs so that the float32 temporary stays small
             step = max(1, (1 << 26) // max(1, math.prod(shp[1:])))
