@@ -394,3 +394,134 @@ def run_workload(name: str, layers: int = 0, new: int = 0) -> Dict[str, object]:
             "generated_per_s": round(sum(r.num_tokens for r in out) / dt, 1),
             "steps": st["steps"], "preemptions": st["preemptions"], "decode_tps": st.get("decode_tps"),
             "prefill_tps": st.get("prefill_tps"), "decode_graphs": len(runner._graphs)}
+
+
+# ------------------------------------------------------------------------------- two designs at equal layer sizes
+
+# Layer sizes that resemble real models: (width, feed-forward, heads of 128).  Every fourth layer of the Pisatar model
+# is the sum of attention and matrix memory, the one before it the delta rule, the others retention.
+DESIGN_SIZES = {
+    "1k": dict(width=1024, ff=3072, heads=8, kv_heads=2, layers=8, vocab=32768),
+    "2k": dict(width=2048, ff=6144, heads=16, kv_heads=4, layers=8, vocab=32768),
+    "4k": dict(width=4096, ff=12288, heads=32, kv_heads=8, layers=4, vocab=32768),
+}
+
+
+def pisatar_raw_config(width: int, ff: int, heads: int, kv_heads: int, layers: int, vocab: int) -> dict:
+    """A Pisatar configuration whose mixers carry as many heads of 128 as the attention of a Qwen3 model of this width."""
+    mlp = {"kind": "dense", "ff": ff}
+    retention = {"type": "retention", "mlp": mlp,
+                 "mixer": {"heads": heads, "dim": 128, "vdim": 128, "rot": {"base": 1e6, "dims": 128},
+                           "decay": [1.0 - 2.0 ** -(5 + 4 * i / max(1, heads - 1)) for i in range(heads)]}}
+    delta = {"type": "channel_delta", "mlp": mlp,
+             "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}}
+    both = {"type": "parallel", "mlp": mlp,
+            "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                               "rot": {"base": 1e4, "dims": 64,
+                                       "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}},
+                      "right": {"heads": heads // 2, "dim": 128, "vdim": 256, "gate_cap": 15.0},
+                      "left_scale": 1.0, "right_scale": 1.0}}
+    pattern = [retention, retention, delta, both]
+    return {"architecture": "Pisatar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [pattern[i % 4] for i in range(layers)]}
+
+
+def step_kernel_times(fn, steps: int) -> Dict[str, float]:
+    """Device milliseconds per call of ``fn`` by kernel name (torch.profiler, CUDA activity only)."""
+    from collections import defaultdict
+    from torch.profiler import ProfilerActivity, profile
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA], record_shapes=False) as prof:
+        for _ in range(steps):
+            fn()
+        torch.cuda.synchronize()
+    out = defaultdict(float)
+    for e in prof.key_averages():
+        us = getattr(e, "self_device_time_total", 0) or getattr(e, "self_cuda_time_total", 0)
+        if us > 0:
+            out[e.key] += us / 1e3 / steps
+    return dict(out)
+
+
+def _kernel_ms(times: Dict[str, float], *needles: str) -> float:
+    return sum(ms for name, ms in times.items() if any(n in name for n in needles))
+
+
+def measure_design(cfg, tokens: int, batch: int, steps: int, warmup: int, page: int = 16) -> Dict[str, object]:
+    """Prefill of one prompt of ``tokens`` and decode steps of ``batch`` requests behind prompts of ``tokens``, with the
+    device time of each by kernel."""
+    from .engine.config import EngineConfig
+    from .engine.runner import ModelRunner
+    pool = batch * ((tokens + 2 * (warmup + steps) + 64 + 63) // 64 * 64) + 2 * tokens
+    ecfg = EngineConfig(max_token=pool, max_reside=batch + 1, page_size=page, prefill_chunk=8192, dtype="bfloat16",
+                        max_model_len=tokens + 2 * (warmup + steps) + 64, use_cuda_graph=True, seed=4)
+    runner = ModelRunner.from_random(cfg, ecfg, seed=4)
+    pf = prefill_throughput(runner, tokens, iters=max(3, steps // 8), warmup=3)
+    gen = torch.Generator().manual_seed(7)
+
+    def one_prefill():
+        runner.add_request("p")
+        runner.step([runner.reserve("p", _random_ids(runner.vocab_size, tokens, gen), [tokens - 1])])
+        runner.free_request("p")
+    pf_kernels = step_kernel_times(one_prefill, 2)
+    dec = decode_throughput(runner, batch, tokens, steps, warmup)
+    rids = fill_requests(runner, batch, tokens, prefix="k")
+    toks = _random_ids(runner.vocab_size, batch, gen)
+
+    def one_decode():
+        runner.step([runner.reserve(rid, [toks[i]], [0]) for i, rid in enumerate(rids)])
+    for _ in range(3):
+        one_decode()
+    dec_kernels = step_kernel_times(one_decode, 8)
+    for rid in rids:
+        runner.free_request(rid)
+    del runner
+    torch.cuda.empty_cache()
+    top = lambda d: {k[:60]: round(v, 4) for k, v in sorted(d.items(), key=lambda kv: -kv[1])[:8]}
+    return {"prefill_tokens_per_s": round(pf["tokens_per_s"], 1), "prefill_ms": round(pf["ms"], 3),
+            "decode_tokens_per_s": round(dec["tokens_per_s"], 1), "decode_ms": round(dec["ms_per_step"], 4),
+            "prefill_kernels": pf_kernels, "decode_kernels": dec_kernels,
+            "prefill_top": top(pf_kernels), "decode_top": top(dec_kernels)}
+
+
+def compare_designs(size: str, tokens: int, batch: int, steps: int, warmup: int, hbm_gbs: float, bf16_tflops: float):
+    """The Pisatar design beside the Qwen3 decoder at equal width, feed-forward, layer count and heads: throughput of
+    both, and how far the kernel that mixes tokens is from its roofline in each (the scan over matrix states against
+    the attention over cached keys).  Rooflines: decode kernels against the copy bandwidth (the state read and written
+    once, the keys and values read once); prefill kernels against the tensor peak for the attention (causal half of
+    4 T^2 heads dim) and against the same peak for the scan (4 to 6 T heads dim vdim, which the scan runs in float32
+    on the CUDA cores)."""
+    from .config.model_config import Qwen3Config
+    from .config.pisatar_config import PisatarConfig
+    sz = DESIGN_SIZES[size]
+    W, ff, H, G, L, V = sz["width"], sz["ff"], sz["heads"], sz["kv_heads"], sz["layers"], sz["vocab"]
+    new = measure_design(PisatarConfig(pisatar_raw_config(W, ff, H, G, L, V)), tokens, batch, steps, warmup)
+    old = measure_design(Qwen3Config.from_dict(dict(vocab_size=V, hidden_size=W, intermediate_size=ff, num_hidden_layers=L,
+                                                    num_attention_heads=H, num_key_value_heads=G, head_dim=128,
+                                                    rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                                                    max_position_embeddings=32768)), tokens, batch, steps, warmup)
+    D = 128
+    n_ret, n_delta, n_both = (L + 3) // 4 + (L + 2) // 4, (L + 1) // 4, L // 4
+    state_bytes = 4 * D * (n_ret * H * 128 + n_delta * H * 128 + n_both * (H // 2) * 256)      # per request, all layers
+    scan_flops = tokens * D * (4.0 * n_ret * H * 128 + 6.0 * n_delta * H * 128 + 4.0 * n_both * (H // 2) * 256)
+    kv_bytes = lambda layers: 2 * 2 * G * D * tokens * batch * layers
+    attn_flops = lambda layers: 4.0 * tokens * tokens * H * D / 2 * layers
+    scan_dec = _kernel_ms(new["decode_kernels"], "linear_scan")
+    scan_pf = _kernel_ms(new["prefill_kernels"], "linear_scan")
+    att_dec_new = _kernel_ms(new["decode_kernels"], "attn_decode", "attn_combine")
+    att_dec_old = _kernel_ms(old["decode_kernels"], "attn_decode", "attn_combine")
+    att_pf_new = _kernel_ms(new["prefill_kernels"], "attn_prefill", "attention_tc5", "tc5_merge")
+    att_pf_old = _kernel_ms(old["prefill_kernels"], "attn_prefill", "attention_tc5", "tc5_merge")
+    frac = lambda work, ms, peak: round(work / (ms * 1e-3) / peak, 4) if ms > 0 else None
+    kernels = {
+        "decode_scan": {"ms": round(scan_dec, 4), "of_hbm": frac(2.0 * state_bytes * batch, scan_dec, hbm_gbs * 1e9)},
+        "decode_attention_pisatar": {"ms": round(att_dec_new, 4), "of_hbm": frac(kv_bytes(n_both), att_dec_new, hbm_gbs * 1e9)},
+        "decode_attention_qwen3": {"ms": round(att_dec_old, 4), "of_hbm": frac(kv_bytes(L), att_dec_old, hbm_gbs * 1e9)},
+        "prefill_scan": {"ms": round(scan_pf, 4), "of_bf16_peak": frac(scan_flops, scan_pf, bf16_tflops * 1e12)},
+        "prefill_attention_pisatar": {"ms": round(att_pf_new, 4), "of_bf16_peak": frac(attn_flops(n_both), att_pf_new, bf16_tflops * 1e12)},
+        "prefill_attention_qwen3": {"ms": round(att_pf_old, 4), "of_bf16_peak": frac(attn_flops(L), att_pf_old, bf16_tflops * 1e12)},
+    }
+    for r in (new, old):
+        del r["prefill_kernels"], r["decode_kernels"]
+    return {"size": size, "width": W, "ff": ff, "heads": H, "kv_heads": G, "layers": L, "tokens": tokens, "batch": batch,
+            "pisatar": new, "qwen3": old, "kernels": kernels}

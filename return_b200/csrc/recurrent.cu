@@ -59,9 +59,12 @@ template <int MODE, int NR>
 __global__ void __launch_bounds__(SCAN_THREADS)
 linear_scan_kernel(const ScanArgs a) {
     constexpr int DP = NR * 8;
-    __shared__ float sq[SCAN_TC][DP];
-    __shared__ float sk[SCAN_TC][DP];
-    __shared__ float sg[MODE == MODE_DELTA ? SCAN_TC : 1][DP];
+    // a token's q, k (and row decays) as [row % 8][row / 8], each run of NR padded by four floats: a thread reads its
+    // NR values as 16-byte pieces, and the eight runs of a warp's request fall on different banks
+    constexpr int RS = NR + 4, DS = 8 * RS;
+    __shared__ __align__(16) float sq[SCAN_TC][DS];
+    __shared__ __align__(16) float sk[SCAN_TC][DS];
+    __shared__ __align__(16) float sg[MODE == MODE_DELTA ? SCAN_TC : 1][DS];
     __shared__ float sv[SCAN_TC][SCAN_COLS];
     __shared__ float sa[SCAN_TC], sb[SCAN_TC];
     const int seg = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * SCAN_COLS;
@@ -93,9 +96,10 @@ linear_scan_kernel(const ScanArgs a) {
             const int tt = e / DP, i = e - tt * DP;
             const size_t t = (size_t)(tc + tt);
             const bool live = i < D;
-            sq[tt][i] = live ? ld_elem(a.q, a.q_f32, t * a.q_ld + (size_t)kvh * D + i) * a.q_scale : 0.f;
-            sk[tt][i] = live ? ld_elem(a.k, a.k_f32, t * a.k_ld + (size_t)kvh * D + i) : 0.f;
-            if (MODE == MODE_DELTA) sg[tt][i] = live ? a.gate_a[(t * H + h) * D + i] : 1.f;
+            const int at = (i & 7) * RS + (i >> 3);
+            sq[tt][at] = live ? ld_elem(a.q, a.q_f32, t * a.q_ld + (size_t)kvh * D + i) * a.q_scale : 0.f;
+            sk[tt][at] = live ? ld_elem(a.k, a.k_f32, t * a.k_ld + (size_t)kvh * D + i) : 0.f;
+            if (MODE == MODE_DELTA) sg[tt][at] = live ? a.gate_a[(t * H + h) * D + i] : 1.f;
         }
         for (int e = tid; e < nt * SCAN_COLS; e += SCAN_THREADS) {
             const int tt = e / SCAN_COLS, c = e - tt * SCAN_COLS;
@@ -116,11 +120,17 @@ linear_scan_kernel(const ScanArgs a) {
         for (int tt = 0; tt < nt; ++tt) {
             const float vj = sv[tt][jj];
             float o = 0.f;
+            float kr[NR], qr[NR];
+#pragma unroll
+            for (int i4 = 0; i4 < NR; i4 += 4) {
+                *(float4*)&kr[i4] = *(const float4*)&sk[tt][r * RS + i4];
+                *(float4*)&qr[i4] = *(const float4*)&sq[tt][r * RS + i4];
+            }
             if (MODE == MODE_DECAY) {
 #pragma unroll
                 for (int ii = 0; ii < NR; ++ii) {
-                    S[ii] = fmaf(decay, S[ii], sk[tt][ii * 8 + r] * vj);
-                    o = fmaf(S[ii], sq[tt][ii * 8 + r], o);
+                    S[ii] = fmaf(decay, S[ii], kr[ii] * vj);
+                    o = fmaf(S[ii], qr[ii], o);
                 }
                 o = group8_sum(o);
             } else if (MODE == MODE_MEMORY) {
@@ -131,7 +141,7 @@ linear_scan_kernel(const ScanArgs a) {
                 float nq = 0.f;
 #pragma unroll
                 for (int ii = 0; ii < NR; ++ii) {
-                    const float bk = fb * sk[tt][ii * 8 + r], qi = sq[tt][ii * 8 + r];
+                    const float bk = fb * kr[ii], qi = qr[ii];
                     S[ii] = fmaf(fa, S[ii], bk * vj);
                     n[ii] = fmaf(fa, n[ii], bk);
                     o = fmaf(S[ii], qi, o);
@@ -143,16 +153,18 @@ linear_scan_kernel(const ScanArgs a) {
             } else {
                 float kv = 0.f;
 #pragma unroll
-                for (int ii = 0; ii < NR; ++ii) {
-                    S[ii] *= sg[tt][ii * 8 + r];
-                    kv = fmaf(S[ii], sk[tt][ii * 8 + r], kv);
+                for (int i4 = 0; i4 < NR; i4 += 4) {
+                    const float4 g4 = *(const float4*)&sg[tt][r * RS + i4];
+                    S[i4] *= g4.x; S[i4 + 1] *= g4.y; S[i4 + 2] *= g4.z; S[i4 + 3] *= g4.w;
                 }
+#pragma unroll
+                for (int ii = 0; ii < NR; ++ii) kv = fmaf(S[ii], kr[ii], kv);
                 kv = group8_sum(kv);
                 const float u = sb[tt] * (vj - kv);
 #pragma unroll
                 for (int ii = 0; ii < NR; ++ii) {
-                    S[ii] = fmaf(sk[tt][ii * 8 + r], u, S[ii]);
-                    o = fmaf(S[ii], sq[tt][ii * 8 + r], o);
+                    S[ii] = fmaf(kr[ii], u, S[ii]);
+                    o = fmaf(S[ii], qr[ii], o);
                 }
                 o = group8_sum(o);
             }

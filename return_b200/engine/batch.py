@@ -237,6 +237,7 @@ class StaticDecodeBatch:
         self._h["want_rows"][:] = np.arange(n)
         self._h["decode_segs"][:] = np.arange(n)
         self._h["seg_kv_len"][:] = 1
+        self._h["seg_slot"][:] = pad_slot    # before the first fill (the warm-up run of a capture): the state slot of no request
         for bt in self._h_bt:
             bt[:] = -1                       # before the first fill: no page is read or written
         self._event = torch.cuda.Event()
