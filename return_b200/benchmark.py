@@ -396,6 +396,42 @@ def run_workload(name: str, layers: int = 0, new: int = 0) -> Dict[str, object]:
             "prefill_tps": st.get("prefill_tps"), "decode_graphs": len(runner._graphs)}
 
 
+def kernel_scan(mode=0, batch=1, tokens=2048, heads=16, kv_heads=0, dim=128, vdim=128, iters=10, warmup=3) -> Dict[str, object]:
+    """The recurrence kernel of the mixers with a matrix state alone: ``batch`` segments of ``tokens`` tokens each
+    (tokens = 1: a decode step).  mode 0: fixed decay, 1: matrix memory, 2: delta rule.  Reports the time of a launch,
+    the float32 operations per second, and the bandwidth on the states (each read and written once)."""
+    from types import SimpleNamespace
+    from .ext import ops
+    dev = torch.device("cuda:0")
+    G = kv_heads or heads
+    T = batch * tokens
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+    unit = lambda x, n: torch.nn.functional.normalize(x.view(T, -1, n), dim=-1).reshape(T, -1)
+    q, k, v = unit(rnd(T, G * dim), dim), unit(rnd(T, G * dim), dim), rnd(T, heads * vdim)
+    pad = (dim + 7) // 8 * 8
+    s_floats = heads * pad * vdim
+    n_off, m_off = s_floats, s_floats + heads * pad
+    copies = max(1, _copies_beyond_l2(batch * (m_off + heads) * 4)) if tokens == 1 else 1
+    states = [torch.zeros((batch, m_off + heads), device=dev) for _ in range(copies)]
+    i32 = lambda x: torch.as_tensor(x, dtype=torch.int32, device=dev)
+    b = SimpleNamespace(cu_q=i32([i * tokens for i in range(batch + 1)]), seg_slot=i32(list(range(batch))), num_segments=batch)
+    if mode == ops.SCAN_DECAY:
+        ga, gb = torch.linspace(0.97, 0.999, heads, device=dev), None
+    elif mode == ops.SCAN_MEMORY:
+        ga, gb = rnd(T, 2 * heads), torch.zeros(2 * heads, device=dev)
+    else:
+        ga, gb = torch.sigmoid(rnd(T, heads * dim) + 3.0).contiguous(), torch.sigmoid(rnd(T, heads)).contiguous()
+    out = torch.empty((T, heads * vdim), device=dev)
+    fns = [(lambda st=st: ops.linear_scan(mode, q, k, v, ga, gb, st, (0, n_off, m_off), b, out, heads, G, dim, vdim,
+                                          q_scale=dim ** -0.5, cap=15.0)) for st in states]
+    ms = _time_kernels(fns, iters, warmup)
+    flops = T * heads * dim * vdim * (6.0 if mode == ops.SCAN_DELTA else 4.0)
+    return {"kernel": "linear_scan", "mode": mode, "batch": batch, "tokens": tokens, "heads": heads, "dim": dim, "vdim": vdim,
+            "ms": round(ms, 4), "ns_per_token": round(ms * 1e6 / tokens, 1), "tflops_f32": round(flops / ms / 1e9, 3),
+            "state_gbs": round(2.0 * batch * s_floats * 4 / ms / 1e6, 1)}
+
+
 # ------------------------------------------------------------------------------- two designs at equal layer sizes
 
 # Layer sizes that resemble real models: (width, feed-forward, heads of 128).  Every fourth layer of the Pisatar model
