@@ -17,7 +17,9 @@
 // spread a head of a long prompt over two and four times as many SMs, were measured slower: 0.64 and 0.76 ms against
 // 0.47 for 2,048 tokens of 16 heads, because the longer chain of shuffles is what a token waits for.)  The state of a
 // request lives in its slot in the same order, [head][row / 8][column][row % 8], which makes a warp's loads and
-// stores of it whole 128-byte lines.
+// stores of it whole 128-byte lines.  A twin of the kernel for steps of single tokens (nothing staged, every thread
+// loading its rows of q and k itself) was measured too: 26 / 20 / 10 us against 7 / 15 / 11 for 8 requests of 16
+// heads (fixed decay / matrix memory / delta rule), 171 / 135 / 65 against 42 / 99 / 75 for 64; not kept.
 #include "common.cuh"
 
 #define SCAN_THREADS 256
@@ -59,7 +61,7 @@ __device__ __forceinline__ float logsigmoid_f(float x) { return x < 0.f ? x - lo
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 template <int MODE, int NR, int R>
-__global__ void __launch_bounds__(SCAN_THREADS)
+__global__ void __launch_bounds__(SCAN_THREADS, NR <= 16 ? 2 : 1)
 linear_scan_kernel(const ScanArgs a) {
     constexpr int DP = NR * R;                         // rows the threads of a column can hold
     constexpr int SCAN_COLS = SCAN_THREADS / R;        // value columns of a CTA
@@ -101,6 +103,7 @@ linear_scan_kernel(const ScanArgs a) {
         m = st[a.m_off + h];
     }
     const float decay = MODE == MODE_DECAY ? a.gate_a[h] : 0.f;
+    const float bias_i = MODE == MODE_MEMORY ? a.gate_b[h] : 0.f, bias_f = MODE == MODE_MEMORY ? a.gate_b[H + h] : 0.f;
 
     // A chunk of up to SCAN_TC tokens comes from global memory into registers while the chunk before it is worked on,
     // and goes to shared memory when that is done.  The registers hold the loaded bits untouched: a conversion or a
@@ -149,8 +152,8 @@ linear_scan_kernel(const ScanArgs a) {
         if (tid < SCAN_TC * SCAN_COLS) sv[tid / SCAN_COLS][tid % SCAN_COLS] = cooked(rv, a.v_f32);
         if (tid < SCAN_TC) {
             if (MODE == MODE_MEMORY) {
-                sa[tid] = a.cap * tanhf((ra + a.gate_b[h]) / a.cap);
-                sb[tid] = logsigmoid_f(a.cap * tanhf((rb + a.gate_b[H + h]) / a.cap));
+                sa[tid] = a.cap * tanhf((ra + bias_i) / a.cap);
+                sb[tid] = logsigmoid_f(a.cap * tanhf((rb + bias_f) / a.cap));
             } else {
                 sb[tid] = rb;
             }
@@ -295,6 +298,41 @@ RB_EXPORT int rb_linear_scan(int mode, const void* q, const void* k, const void*
     return (int)cudaErrorInvalidValue;
 }
 
+// ---------------------------------------------------------------- a long segment cut into pieces that are scanned side by side
+// With a fixed decay the state after a piece of n tokens is decay^n * (state before it) + (what the piece alone leaves
+// behind, scanned from zero).  So the pieces of a long segment can be scanned from zero all at once; this kernel then
+// walks a segment's pieces in order, puts the state each piece starts from where the piece's own result was
+// (pieces[p] <- carry; carry <- decay^n carry + pieces[p]) and leaves the last carry in the request's slot; a second
+// scan of the pieces from those states gives the outputs.  One thread an element of the state.
+__global__ void scan_pieces_combine_kernel(float* __restrict__ pieces, long long piece_stride, float* __restrict__ state,
+                                           long long state_stride, int s_off, const float* __restrict__ decay,
+                                           const int* __restrict__ cu_piece, const int* __restrict__ seg_first,
+                                           const int* __restrict__ seg_slot, int per_head, int total) {
+    pdl_wait();
+    const int seg = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total) return;
+    const float log_decay = logf(decay[e / per_head]);
+    float* home = state + (long long)seg_slot[seg] * state_stride + s_off + e;
+    float carry = *home;
+    for (int p = seg_first[seg]; p < seg_first[seg + 1]; ++p) {
+        float* at = pieces + (long long)p * piece_stride + e;
+        const float left = *at;
+        *at = carry;
+        carry = fmaf(expf((float)(cu_piece[p + 1] - cu_piece[p]) * log_decay), carry, left);
+    }
+    *home = carry;
+}
+
+RB_EXPORT int rb_scan_pieces_combine(float* pieces, long long piece_stride, float* state, long long state_stride, int s_off,
+                                     const float* decay, const int* cu_piece, const int* seg_first, const int* seg_slot,
+                                     int per_head, int total, int segments, cudaStream_t st) {
+    if (segments <= 0 || total <= 0) return 0;
+    dim3 grid((total + 255) / 256, segments);
+    return rb_launch_pdl(scan_pieces_combine_kernel, grid, dim3(256), 0, st, pieces, piece_stride, state, state_stride, s_off,
+                         decay, cu_piece, seg_first, seg_slot, per_head, total);
+}
+
 // ---------------------------------------------------------------- rotation of q and k into float32
 // x: two runs of `heads` heads of size D inside rows of a projection buffer (q at q_off, k at k_off).  The first
 // `rot` elements of a head turn by the angle of the token's position (tables cos, sin [positions, rot/2]), element
@@ -343,6 +381,35 @@ RB_EXPORT int rb_rotary_to_f32(const void* x, int ld, int q_off, int k_off, cons
         rb_launch_pdl(rotary_to_f32_kernel<bf16>, dim3(grid), dim3(threads), 0, st, (const bf16*)x, ld, q_off, k_off, cos_t, sin_t, rot, pos,
                                                             q32, k32, heads, D, q_scale, k_scale);
     return rb_launch_status();
+}
+
+// The same rotation in place, on the q and k heads of a packed [q heads | k heads | ...] row of the activation type,
+// for rotary widths that the rotation-and-cache-write kernel does not take (any even width).  A thread owns a pair.
+template <typename TA>
+__global__ void rotary_inplace_kernel(TA* __restrict__ x, int ld, const float* __restrict__ cos_t,
+                                      const float* __restrict__ sin_t, int rot, const int* __restrict__ pos,
+                                      int heads, int D) {
+    pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y;            // h over q heads, then k heads
+    const int half = rot >> 1;
+    TA* row = x + (size_t)t * ld + (size_t)h * D;
+    const int p = pos[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float c = cos_t[(size_t)p * half + i], s = sin_t[(size_t)p * half + i];
+        const float u = to_f32(row[i]), v = to_f32(row[i + half]);
+        row[i] = from_f32<TA>(u * c - v * s);
+        row[i + half] = from_f32<TA>(v * c + u * s);
+    }
+}
+
+RB_EXPORT int rb_rotary_inplace(void* x, int ld, const float* cos_t, const float* sin_t, int rot, const int* pos,
+                                int act_dtype, int T, int heads, int D, cudaStream_t st) {
+    if (T <= 0 || rot <= 0) return 0;
+    if (rot > D || (rot & 1)) return (int)cudaErrorInvalidValue;
+    dim3 grid(T, heads);
+    if (act_dtype == RB_F32)
+        return rb_launch_pdl(rotary_inplace_kernel<float>, grid, dim3(32), 0, st, (float*)x, ld, cos_t, sin_t, rot, pos, heads, D);
+    return rb_launch_pdl(rotary_inplace_kernel<bf16>, grid, dim3(32), 0, st, (bf16*)x, ld, cos_t, sin_t, rot, pos, heads, D);
 }
 
 // ---------------------------------------------------------------- what the delta rule needs of a token

@@ -763,6 +763,10 @@ def recurrent_lib() -> ctypes.CDLL:
         P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
         lib.rb_linear_scan.argtypes = [I, P, P, P, I, I, I, I, I, I, P, P, F, F, P, L, I, I, I, P, P, P, I, I, I, I, I, P]
         lib.rb_rotary_to_f32.argtypes = [P, I, I, I, P, P, I, P, P, P, I, I, I, I, F, F, P]
+        lib.rb_scan_pieces_combine.argtypes = [P, L, P, L, I, P, P, P, P, I, I, I, P]
+        lib.rb_scan_pieces_combine.restype = c_int
+        lib.rb_rotary_inplace.argtypes = [P, I, P, P, I, P, I, I, I, I, P]
+        lib.rb_rotary_inplace.restype = c_int
         lib.rb_delta_prep.argtypes = [P, I, P, I, I, P, L, I, P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, P]
         lib.rb_conv_state_update.argtypes = [P, I, I, P, L, I, P, P, I, I, I, P]
         lib.rb_head_norm_gate.argtypes = [P, P, I, P, I, I, I, F, P, I, I, I, I, P]
@@ -806,6 +810,18 @@ def linear_scan(mode: int, q, k, v, gate_a, gate_b, state, offsets, batch, out, 
         "linear_scan")
 
 
+def scan_pieces_combine(pieces, state, s_off: int, decay, cu_piece, seg_first, seg_slot, per_head: int, total: int,
+                        segments: int) -> None:
+    """For a fixed-decay state whose long segments were scanned in pieces from zero: per segment, in order,
+    ``pieces[p] <- carry; carry <- decay^len(p) * carry + pieces[p]``, starting from the request's state and leaving the
+    last carry there.  pieces: float32 [n_pieces, >= total]; per_head: state elements of one head."""
+    assert pieces.dtype == state.dtype == decay.dtype == torch.float32 and pieces.is_contiguous() and state.is_contiguous()
+    assert cu_piece.dtype == seg_first.dtype == seg_slot.dtype == torch.int32
+    _check(recurrent_lib().rb_scan_pieces_combine(_ptr(pieces), pieces.stride(0), _ptr(state), state.stride(0), s_off,
+                                                  _ptr(decay), _ptr(cu_piece), _ptr(seg_first), _ptr(seg_slot), per_head,
+                                                  total, segments, _stream()), "scan_pieces_combine")
+
+
 def rotary_to_f32(x, q_off: int, k_off: int, cos, sin, rot: int, pos, q32, k32, heads: int, dim: int,
                   q_scale: float = 1.0, k_scale: float = 1.0) -> None:
     """q and k heads of the projection rows ``x`` (q at column q_off, k at k_off), turned by their positions on the
@@ -819,6 +835,14 @@ def rotary_to_f32(x, q_off: int, k_off: int, cos, sin, rot: int, pos, q32, k32, 
     _check(recurrent_lib().rb_rotary_to_f32(_ptr(x), x.stride(0), q_off, k_off, _ptr(cos), _ptr(sin), rot, _ptr(pos),
                                             _ptr(q32), _ptr(k32), dtype_code(x.dtype), T, heads, dim, q_scale, k_scale,
                                             _stream()), "rotary_to_f32")
+
+
+def rotary_inplace(x, cos, sin, rot: int, pos, heads: int, dim: int) -> None:
+    """The first ``heads`` heads of every row of ``x`` turned in place by their positions (first ``rot`` elements of a
+    head, element i with i + rot/2); any even ``rot``."""
+    assert x.stride(1) == 1 and cos.dtype == sin.dtype == torch.float32 and cos.shape[1] * 2 == rot
+    _check(recurrent_lib().rb_rotary_inplace(_ptr(x), x.stride(0), _ptr(cos), _ptr(sin), rot, _ptr(pos),
+                                             dtype_code(x.dtype), x.shape[0], heads, dim, _stream()), "rotary_inplace")
 
 
 def delta_prep(x, taps, state, conv_off: int, batch, q32, k32, v32, a, A_log, dt_bias, b, heads: int, kv_heads: int,

@@ -12,6 +12,9 @@ zeroed when a request takes it, which is every part's starting state.
 """
 from __future__ import annotations
 
+from types import SimpleNamespace
+
+import numpy as np
 import torch
 
 from ..ext import ops
@@ -49,7 +52,7 @@ class Retention(_StateMixer):
         if len(spec.decay) != spec.num_heads:
             raise ValueError(f"{len(spec.decay)} decays for {spec.num_heads} heads")
         self.position = POSITION_ENCODINGS.build(spec.position, env) if spec.position is not None else None
-        if self.position is not None and self.position.rotary_tables is None:
+        if self.position is not None and not hasattr(self.position, "tables"):
             raise ValueError("retention rotates pairs of a head: the position encoding must give rotary tables")
         self._decay = None
 
@@ -57,6 +60,43 @@ class Retention(_StateMixer):
         s = self.spec
         return {"in": ParamSpec((2 * self.H * self.D + 2 * self.H * self.V, s.hidden_size)),
                 "o": ParamSpec((s.hidden_size, self.H * self.V))}
+
+    # A segment of at least this many tokens is cut into pieces that are scanned side by side (bfloat16 path only:
+    # the sums then take another order than token by token, which the float32 path never does).
+    PIECES_MIN_TOKENS = 1024
+    PIECE_MIN_TOKENS = 128
+
+    def _pieces(self, batch):
+        """None, or (a batch whose segments are the pieces, first piece of every segment, number of pieces) when the
+        step holds a long segment and its CTAs alone would leave most SMs idle.  Worked out once per step."""
+        host = getattr(batch, "host", None)
+        if host is None or not getattr(host, "num_multi", 0):
+            return None
+        memo = getattr(batch, "scratch", None)
+        key = ("retention.pieces.plan", self.H, self.V)
+        if memo is not None and key in memo:
+            return memo[key]
+        plan = None
+        lens = np.diff(host.cu_q).astype(np.int64)
+        if int(lens.max()) >= self.PIECES_MIN_TOKENS:
+            ctas = self.H * ((self.V + 31) // 32)
+            want = (2 * ops.num_sms()) // max(1, ctas * int((lens >= self.PIECES_MIN_TOKENS).sum()))
+            if want >= 3:                                   # two passes over the tokens: fewer pieces would not pay
+                cuts, first = [0], [0]
+                for start, n in zip(host.cu_q[:-1], lens):
+                    k = int(min(want, max(1, n // self.PIECE_MIN_TOKENS))) if n >= self.PIECES_MIN_TOKENS else 1
+                    edges = [int(start) + (int(n) * i) // k for i in range(1, k + 1)]
+                    cuts.extend(edges)
+                    first.append(first[-1] + k)
+                n_pieces = len(cuts) - 1
+                tables = torch.from_numpy(np.asarray(cuts + first + list(range(n_pieces)), np.int32)).to(
+                    self.env.device, non_blocking=True)
+                a, c = len(cuts), len(cuts) + len(first)
+                virtual = SimpleNamespace(cu_q=tables[:a], seg_slot=tables[c:], num_segments=n_pieces)
+                plan = (virtual, tables[a:c], n_pieces)
+        if memo is not None:
+            memo[key] = plan
+        return plan
 
     def cache_need(self):
         return StateNeed((self.s_floats,), torch.float32)
@@ -69,13 +109,27 @@ class Retention(_StateMixer):
         ops.linear(x, self.p_in, proj)
         q32 = ctx.buffer("retention.q", (T, HD), torch.float32, dev)
         k32 = ctx.buffer("retention.k", (T, HD), torch.float32, dev)
-        cos, sin, rot = self.position.rotary_tables() if self.position is not None else (None, None, 0)
+        cos, sin, rot = self.position.tables() if self.position is not None else (None, None, 0)
         ops.rotary_to_f32(proj, 0, HD, cos, sin, rot, b.pos, q32, k32, self.H, self.D, 1.0, self.D ** -0.5)
         if self._decay is None:
             self._decay = torch.tensor(s.decay, dtype=torch.float32, device=dev)
         o = ctx.buffer("retention.o", (T, HV), torch.float32, dev)
-        ops.linear_scan(ops.SCAN_DECAY, q32, k32, proj[:, 2 * HD:2 * HD + HV], self._decay, None, ctx.state,
-                        (0, 0, 0), b, o, self.H, self.H, self.D, self.V)
+        v = proj[:, 2 * HD:2 * HD + HV]
+        pieces = self._pieces(b) if x.dtype != torch.float32 else None
+        if pieces is None:
+            ops.linear_scan(ops.SCAN_DECAY, q32, k32, v, self._decay, None, ctx.state, (0, 0, 0), b, o,
+                            self.H, self.H, self.D, self.V)
+        else:
+            # long segments in pieces side by side: scan every piece from zero, hand the states on in order, scan again
+            virtual, seg_first, n_pieces = pieces
+            held = ctx.buffer("retention.pieces", (n_pieces, self.s_floats), torch.float32, dev)
+            held.zero_()
+            for _ in range(2):
+                ops.linear_scan(ops.SCAN_DECAY, q32, k32, v, self._decay, None, held, (0, 0, 0), virtual, o,
+                                self.H, self.H, self.D, self.V)
+                if _ == 0:
+                    ops.scan_pieces_combine(held, ctx.state, 0, self._decay, virtual.cu_q, seg_first, b.seg_slot,
+                                            _pad8(self.D) * self.V, self.s_floats, b.num_segments)
         mixed = ctx.buffer("retention.mixed", (T, HV), x.dtype, dev)
         ops.head_norm_gate(o, proj[:, 2 * HD + HV:], None, 0, 0, s.eps, mixed, self.H, self.V)
         return self._project_out(mixed, ctx)

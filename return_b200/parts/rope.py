@@ -42,6 +42,8 @@ class RotaryEncoding(PositionEncoding):
             self._tables = shared
         return self._tables
 
+    tables = rotary_tables
+
 
 @POSITION_ENCODINGS.register("rope_scaled")
 class ScaledRotaryEncoding(PositionEncoding):
@@ -67,6 +69,16 @@ class ScaledRotaryEncoding(PositionEncoding):
         return f
 
     def rotary_tables(self):
+        """(cos, sin, rotary_dim) for the kernel that rotates while it writes the cache, which takes widths that are
+        multiples of 4; None for any other even width: the attention then calls ``apply``."""
+        return self.tables() if self.spec.rotary_dim % 4 == 0 else None
+
+    def apply(self, qkv, batch, num_heads, num_kv_heads, head_dim):
+        from ..ext import ops
+        cos, sin, rot = self.tables()
+        ops.rotary_inplace(qkv, cos, sin, rot, batch.pos, num_heads + num_kv_heads, head_dim)
+
+    def tables(self):
         if self._tables is None:
             s = self.spec
             key = ("scaled", s.rotary_dim, float(s.theta), s.scaling, s.max_positions, str(self.env.device))

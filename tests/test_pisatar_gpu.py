@@ -4,7 +4,7 @@ Every test makes a small configuration of its own with random weights (written a
 model folder holds them), replays a trace through the engine's step function and compares every logits row with the
 plain implementation's, which walks the whole sequence in float64.  float32 path: every row within 1e-4 of its size.
 bfloat16 path: rounding is amplified at single positions (a read-out that is divided by a small root mean square or
-a small normaliser), so the rows are judged together: their mean error below 3 %, at most one row in fifty beyond a
+a small normaliser), so the rows are weighed together: their mean error below 3 %, at most one row in fifty beyond a
 twelfth of its size, none beyond a third.  A lost key, a lost state or a wrong position moves every row behind it.
 """
 import json
@@ -174,6 +174,7 @@ ALONE = {
     "attention_and_memory": lambda: config([parallel_layer()]),
     "attention_equal_sizes": lambda: config([parallel_layer(dim=32, vdim=32, rot=32, scaling=False, scales=(1.0, 0.0))]),
     "memory_mostly": lambda: config([parallel_layer(scales=(0.0, 1.0), cap=2.0)]),
+    "rotary_widths_of_six_and_ten": lambda: config([parallel_layer(rot=6), retention_layer(rot=10)]),
     "layer_run_twice": lambda: config([delta_layer(), delta_layer(weights_of=0), retention_layer(), retention_layer(weights_of=2)]),
 }
 
@@ -273,6 +274,33 @@ def test_long_decoding(tmp_path_factory, dtype, graph):
         assert_close(got[rid], plain_rows(entry, ids)[2:], dtype, rid)
 
 
+def test_a_long_prompt_scanned_in_pieces_side_by_side(tmp_path_factory):
+    """On the bfloat16 path a retention cuts a portion of 1,024 tokens or more into pieces that are scanned at the same
+    time, hands the states from piece to piece and scans again.  The outputs of every piece, the state that the tokens
+    decoded afterwards start from, and a short request in the same step must all be right; the decays are slow, so a
+    state handed on wrongly would show to the end."""
+    raw = config([retention_layer(heads=2, dim=24, vdim=40, rot=16, decay=[0.999, 0.9995]),
+                  retention_layer(heads=3, dim=16, vdim=16, rot=8, decay=[0.99, 0.999, 0.9999], ff=0)], width=32)
+    entry = model(tmp_path_factory, "pieces", raw)
+    reqs = requests_for(entry, (1300, 40), seed=80)
+    long_ids, short_ids = reqs["r0"], reqs["r1"]
+    steps = [{"step": 0, "entries": [{"id": "r1", "tokens": short_ids[:30], "want": list(range(30))}], "end": []},
+             {"step": 1, "entries": [{"id": "r0", "tokens": long_ids[:100], "want": list(range(100))},
+                                      {"id": "r1", "tokens": short_ids[30:31], "want": [0]}], "end": []},
+             {"step": 2, "entries": [{"id": "r1", "tokens": short_ids[31:32], "want": [0]},
+                                      {"id": "r0", "tokens": long_ids[100:1290], "want": list(range(1190))}], "end": []}]
+    for k in range(8):
+        steps.append({"step": 3 + k, "entries": [{"id": "r0", "tokens": [long_ids[1290 + k]], "want": [0]},
+                                                  {"id": "r1", "tokens": [short_ids[32 + k]], "want": [0]}],
+                      "end": ["r0", "r1"] if k == 7 else []})
+    got = run_trace(entry[0], "bfloat16", steps)
+    assert_close(got["r0"][:1298], plain_rows(entry, long_ids)[:1298], "bfloat16", "long")
+    assert_close(got["r1"], plain_rows(entry, short_ids), "bfloat16", "short")
+    # the walk token by token and the walk in pieces agree to rounding
+    one = run_trace(entry[0], "bfloat16", tail_decoded({"r0": long_ids[:1000]}, tail=8))
+    assert_close(got["r0"][:1000], one["r0"], "bfloat16", "pieces against one walk")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_other_sizes(tmp_path_factory, dtype):
     entry = model(tmp_path_factory, "other", other_sizes_config(), seed=11)
@@ -316,6 +344,19 @@ def test_bfloat16_generation_picks_tokens_the_plain_model_rates_highest(tmp_path
         for k, tok in enumerate(r.output_ids):
             row = lg[len(p) - 1 + k]
             assert row[tok] >= row.max() - 0.1 * row.std(), (k, tok)
+
+
+def test_command_line_generates(tmp_path_factory):
+    import subprocess
+    import sys
+    entry = model(tmp_path_factory, "full", full_config())
+    prompt = requests_for(entry, (9,), seed=60)["r0"]
+    out = subprocess.run([sys.executable, "-m", "return_b200", "generate", "--model", entry[0], "--prompt-ids",
+                          ",".join(map(str, prompt)), "--new", "6", "--temperature", "0", "--dtype", "float32",
+                          "--max-token", "256", "--max-reside", "2"], capture_output=True, text=True, timeout=600,
+                         cwd=helpers.ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert json.loads(out.stdout.strip().splitlines()[0])["output_ids"] == _greedy_plain(entry, prompt, 6)
 
 
 def test_command_line_runs_the_model(tmp_path_factory):
