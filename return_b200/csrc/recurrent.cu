@@ -39,6 +39,7 @@ struct ScanArgs {
     float* state;             // [slots, state_stride]
     long long state_stride;
     int s_off, n_off, m_off;  // where S, n and m start inside a slot's row
+    int f_off;                // matrix memory: where the sum of the segment's log forget gates goes per head, or -1
     const int* cu_q; const int* seg_slot;
     float* out;               // [T, H*V]
     int H, G, D, V;
@@ -88,7 +89,7 @@ linear_scan_kernel(const ScanArgs a) {
     const bool col = j < V;
 
     float S[NR], n[MODE == MODE_MEMORY ? NR : 1];
-    float m = 0.f;
+    float m = 0.f, forgot = 0.f;
 #pragma unroll
     for (int ii = 0; ii < NR; ++ii) {
         const int row = r + R * ii;                    // rows beyond the padded key size do not exist: they stay zero
@@ -184,6 +185,7 @@ linear_scan_kernel(const ScanArgs a) {
             const float m_new = fmaxf(lf + m, li);
             const float fa = expf(lf + m - m_new), fb = expf(li - m_new);
             m = m_new;
+            forgot += lf;
             floor_[tt] = expf(-m_new);
             float n4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -263,7 +265,10 @@ linear_scan_kernel(const ScanArgs a) {
             const int row = r + R * ii;
             if (row < nrd * 8) st[a.n_off + (size_t)h * nrd * 8 + row] = n[ii];
         }
-        if (lane == 0) st[a.m_off + h] = m;
+        if (lane == 0) {
+            st[a.m_off + h] = m;
+            if (a.f_off >= 0) st[a.f_off + h] = forgot;
+        }
     }
 }
 
@@ -284,13 +289,13 @@ static int launch_scan(const ScanArgs& a, int segments, cudaStream_t st) {
 RB_EXPORT int rb_linear_scan(int mode, const void* q, const void* k, const void* v, int q_ld, int k_ld, int v_ld,
                              int q_f32, int k_f32, int v_f32, const float* gate_a, const float* gate_b, float cap,
                              float q_scale, float* state, long long state_stride, int s_off, int n_off, int m_off,
-                             const int* cu_q, const int* seg_slot, float* out, int H, int G, int D, int V,
+                             int f_off, const int* cu_q, const int* seg_slot, float* out, int H, int G, int D, int V,
                              int segments, cudaStream_t st) {
     ScanArgs a;
     a.q = q; a.k = k; a.v = v; a.q_ld = q_ld; a.k_ld = k_ld; a.v_ld = v_ld;
     a.q_f32 = q_f32; a.k_f32 = k_f32; a.v_f32 = v_f32;
     a.gate_a = gate_a; a.gate_b = gate_b; a.cap = cap; a.q_scale = q_scale;
-    a.state = state; a.state_stride = state_stride; a.s_off = s_off; a.n_off = n_off; a.m_off = m_off;
+    a.state = state; a.state_stride = state_stride; a.s_off = s_off; a.n_off = n_off; a.m_off = m_off; a.f_off = f_off;
     a.cu_q = cu_q; a.seg_slot = seg_slot; a.out = out; a.H = H; a.G = G; a.D = D; a.V = V;
     if (mode == MODE_DECAY) return launch_scan<MODE_DECAY>(a, segments, st);
     if (mode == MODE_MEMORY) return launch_scan<MODE_MEMORY>(a, segments, st);
@@ -331,6 +336,64 @@ RB_EXPORT int rb_scan_pieces_combine(float* pieces, long long piece_stride, floa
     dim3 grid((total + 255) / 256, segments);
     return rb_launch_pdl(scan_pieces_combine_kernel, grid, dim3(256), 0, st, pieces, piece_stride, state, state_stride, s_off,
                          decay, cu_piece, seg_first, seg_slot, per_head, total);
+}
+
+// The same for the matrix memory.  A piece scanned from nothing (S = 0, n = 0, m = -infinity) leaves S', n', its own
+// running maximum m' and F, the sum of its log forget gates; behind a state (S0, n0, m0) the piece ends in
+//     m = max(F + m0, m'),   S = e^(F + m0 - m) S0 + e^(m' - m) S',   n likewise.
+// The first kernel walks S and n (one thread an element; it reads every piece's m' and F and writes neither), the
+// second, launched behind it, walks the maxima (one thread a head).
+__global__ void memory_pieces_combine_kernel(float* __restrict__ pieces, long long piece_stride, float* __restrict__ state,
+                                             long long state_stride, int s_off, int n_off, int m_off, int f_off,
+                                             const int* __restrict__ seg_first, const int* __restrict__ seg_slot,
+                                             int per_head_s, int per_head_n, int total_s, int total) {
+    pdl_wait();
+    const int seg = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total) return;
+    const int h = e < total_s ? e / per_head_s : (e - total_s) / per_head_n;
+    const int at = e < total_s ? s_off + e : n_off + (e - total_s);
+    float* home = state + (long long)seg_slot[seg] * state_stride;
+    float carry = home[at], m = home[m_off + h];
+    for (int p = seg_first[seg]; p < seg_first[seg + 1]; ++p) {
+        float* row = pieces + (long long)p * piece_stride;
+        const float left = row[at], m_piece = row[m_off + h], forgot = row[f_off + h];
+        row[at] = carry;
+        const float m_new = fmaxf(forgot + m, m_piece);
+        carry = fmaf(expf(forgot + m - m_new), carry, expf(m_piece - m_new) * left);
+        m = m_new;
+    }
+    home[at] = carry;
+}
+
+__global__ void memory_pieces_maxima_kernel(float* __restrict__ pieces, long long piece_stride, float* __restrict__ state,
+                                            long long state_stride, int m_off, int f_off, const int* __restrict__ seg_first,
+                                            const int* __restrict__ seg_slot, int H) {
+    pdl_wait();
+    const int seg = blockIdx.y, h = blockIdx.x * blockDim.x + threadIdx.x;
+    if (h >= H) return;
+    float* home = state + (long long)seg_slot[seg] * state_stride;
+    float m = home[m_off + h];
+    for (int p = seg_first[seg]; p < seg_first[seg + 1]; ++p) {
+        float* row = pieces + (long long)p * piece_stride;
+        const float m_piece = row[m_off + h], forgot = row[f_off + h];
+        row[m_off + h] = m;
+        m = fmaxf(forgot + m, m_piece);
+    }
+    home[m_off + h] = m;
+}
+
+RB_EXPORT int rb_memory_pieces_combine(float* pieces, long long piece_stride, float* state, long long state_stride, int s_off,
+                                       int n_off, int m_off, int f_off, const int* seg_first, const int* seg_slot,
+                                       int per_head_s, int per_head_n, int H, int segments, cudaStream_t st) {
+    if (segments <= 0) return 0;
+    const int total_s = H * per_head_s, total = total_s + H * per_head_n;
+    int rc = rb_launch_pdl(memory_pieces_combine_kernel, dim3((total + 255) / 256, segments), dim3(256), 0, st, pieces,
+                           piece_stride, state, state_stride, s_off, n_off, m_off, f_off, seg_first, seg_slot, per_head_s,
+                           per_head_n, total_s, total);
+    if (rc) return rc;
+    return rb_launch_pdl(memory_pieces_maxima_kernel, dim3((H + 63) / 64, segments), dim3(64), 0, st, pieces, piece_stride,
+                         state, state_stride, m_off, f_off, seg_first, seg_slot, H);
 }
 
 // ---------------------------------------------------------------- rotation of q and k into float32

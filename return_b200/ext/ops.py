@@ -761,10 +761,12 @@ def recurrent_lib() -> ctypes.CDLL:
     if _recurrent is None:
         lib = build.load("return_recurrent", _RECURRENT_SOURCES, {"RB_PDL_MODE": PDL_MODE})
         P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
-        lib.rb_linear_scan.argtypes = [I, P, P, P, I, I, I, I, I, I, P, P, F, F, P, L, I, I, I, P, P, P, I, I, I, I, I, P]
+        lib.rb_linear_scan.argtypes = [I, P, P, P, I, I, I, I, I, I, P, P, F, F, P, L, I, I, I, I, P, P, P, I, I, I, I, I, P]
         lib.rb_rotary_to_f32.argtypes = [P, I, I, I, P, P, I, P, P, P, I, I, I, I, F, F, P]
         lib.rb_scan_pieces_combine.argtypes = [P, L, P, L, I, P, P, P, P, I, I, I, P]
         lib.rb_scan_pieces_combine.restype = c_int
+        lib.rb_memory_pieces_combine.argtypes = [P, L, P, L, I, I, I, I, P, P, I, I, I, I, P]
+        lib.rb_memory_pieces_combine.restype = c_int
         lib.rb_rotary_inplace.argtypes = [P, I, P, P, I, P, I, I, I, I, P]
         lib.rb_rotary_inplace.restype = c_int
         lib.rb_delta_prep.argtypes = [P, I, P, I, I, P, L, I, P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, P]
@@ -788,7 +790,7 @@ def _is_f32(t: torch.Tensor) -> int:
 
 
 def linear_scan(mode: int, q, k, v, gate_a, gate_b, state, offsets, batch, out, heads: int, kv_heads: int,
-                dim: int, vdim: int, q_scale: float = 1.0, cap: float = 0.0) -> None:
+                dim: int, vdim: int, q_scale: float = 1.0, cap: float = 0.0, forgot_offset: int = -1) -> None:
     """The recurrence of a mixer with a [dim, vdim] state per head, over every segment of the step, token by token.
 
     q, k: [T, >= kv_heads * dim] views (float32 or bfloat16, unit stride along a row), v: [T, >= heads * vdim];
@@ -796,7 +798,8 @@ def linear_scan(mode: int, q, k, v, gate_a, gate_b, state, offsets, batch, out, 
     matrix, the normaliser and the running maximum start inside a row (the last two for ``SCAN_MEMORY`` only).
     ``gate_a`` / ``gate_b`` by mode: SCAN_DECAY: [heads] decays / None; SCAN_MEMORY: [T, 2 heads] gate
     pre-activations (input, forget) / [2 heads] biases; SCAN_DELTA: [T, heads, dim] row decays / [T, heads] beta.
-    out: float32 [T, heads * vdim]."""
+    out: float32 [T, heads * vdim].  ``forgot_offset`` (SCAN_MEMORY): where in a row the sum of the segment's log forget
+    gates is left per head, or -1."""
     assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == heads * vdim
     assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and dim <= SCAN_MAX_KEY_DIM
@@ -806,7 +809,7 @@ def linear_scan(mode: int, q, k, v, gate_a, gate_b, state, offsets, batch, out, 
     _check(recurrent_lib().rb_linear_scan(
         mode, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _is_f32(q), _is_f32(k), _is_f32(v),
         _ptr(gate_a), _ptr(gate_b), cap, q_scale, _ptr(state), state.stride(0), offsets[0], offsets[1], offsets[2],
-        _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(out), heads, kv_heads, dim, vdim, batch.num_segments, _stream()),
+        forgot_offset, _ptr(batch.cu_q), _ptr(batch.seg_slot), _ptr(out), heads, kv_heads, dim, vdim, batch.num_segments, _stream()),
         "linear_scan")
 
 
@@ -820,6 +823,18 @@ def scan_pieces_combine(pieces, state, s_off: int, decay, cu_piece, seg_first, s
     _check(recurrent_lib().rb_scan_pieces_combine(_ptr(pieces), pieces.stride(0), _ptr(state), state.stride(0), s_off,
                                                   _ptr(decay), _ptr(cu_piece), _ptr(seg_first), _ptr(seg_slot), per_head,
                                                   total, segments, _stream()), "scan_pieces_combine")
+
+
+def memory_pieces_combine(pieces, state, offsets, forgot_offset: int, seg_first, seg_slot, per_head_s: int, per_head_n: int,
+                          heads: int, segments: int) -> None:
+    """The matrix memory's counterpart of ``scan_pieces_combine``: pieces scanned from (0, 0, -inf) hold S', n', m' and
+    the sum F of their log forget gates; per segment, in order, every piece gets the state it starts from and the
+    request's slot the state behind the last one.  offsets = (S, n, m) inside a row."""
+    assert pieces.dtype == state.dtype == torch.float32 and pieces.is_contiguous() and state.is_contiguous()
+    _check(recurrent_lib().rb_memory_pieces_combine(_ptr(pieces), pieces.stride(0), _ptr(state), state.stride(0), offsets[0],
+                                                    offsets[1], offsets[2], forgot_offset, _ptr(seg_first), _ptr(seg_slot),
+                                                    per_head_s, per_head_n, heads, segments, _stream()),
+           "memory_pieces_combine", 2)
 
 
 def rotary_to_f32(x, q_off: int, k_off: int, cos, sin, rot: int, pos, q32, k32, heads: int, dim: int,

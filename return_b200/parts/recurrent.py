@@ -38,29 +38,6 @@ class _StateMixer(Mixer):
     def out_projection(self):
         return self.p_o
 
-    def _project_out(self, mixed, ctx):
-        y = ctx.buffer(self.spec.kind + ".y", (mixed.shape[0], self.spec.hidden_size), torch.float32, mixed.device)
-        ops.linear(mixed, self.p_o, y)
-        return y
-
-
-@MIXERS.register("retention")
-class Retention(_StateMixer):
-    def __init__(self, spec, env):
-        super().__init__(spec, env)
-        self._sizes()
-        if len(spec.decay) != spec.num_heads:
-            raise ValueError(f"{len(spec.decay)} decays for {spec.num_heads} heads")
-        self.position = POSITION_ENCODINGS.build(spec.position, env) if spec.position is not None else None
-        if self.position is not None and not hasattr(self.position, "tables"):
-            raise ValueError("retention rotates pairs of a head: the position encoding must give rotary tables")
-        self._decay = None
-
-    def params(self):
-        s = self.spec
-        return {"in": ParamSpec((2 * self.H * self.D + 2 * self.H * self.V, s.hidden_size)),
-                "o": ParamSpec((s.hidden_size, self.H * self.V))}
-
     # A segment of at least this many tokens is cut into pieces that are scanned side by side (bfloat16 path only:
     # the sums then take another order than token by token, which the float32 path never does).
     PIECES_MIN_TOKENS = 1024
@@ -73,7 +50,7 @@ class Retention(_StateMixer):
         if host is None or not getattr(host, "num_multi", 0):
             return None
         memo = getattr(batch, "scratch", None)
-        key = ("retention.pieces.plan", self.H, self.V)
+        key = ("state_mixer.pieces.plan", self.H, self.V)
         if memo is not None and key in memo:
             return memo[key]
         plan = None
@@ -97,6 +74,30 @@ class Retention(_StateMixer):
         if memo is not None:
             memo[key] = plan
         return plan
+
+
+    def _project_out(self, mixed, ctx):
+        y = ctx.buffer(self.spec.kind + ".y", (mixed.shape[0], self.spec.hidden_size), torch.float32, mixed.device)
+        ops.linear(mixed, self.p_o, y)
+        return y
+
+
+@MIXERS.register("retention")
+class Retention(_StateMixer):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self._sizes()
+        if len(spec.decay) != spec.num_heads:
+            raise ValueError(f"{len(spec.decay)} decays for {spec.num_heads} heads")
+        self.position = POSITION_ENCODINGS.build(spec.position, env) if spec.position is not None else None
+        if self.position is not None and not hasattr(self.position, "tables"):
+            raise ValueError("retention rotates pairs of a head: the position encoding must give rotary tables")
+        self._decay = None
+
+    def params(self):
+        s = self.spec
+        return {"in": ParamSpec((2 * self.H * self.D + 2 * self.H * self.V, s.hidden_size)),
+                "o": ParamSpec((s.hidden_size, self.H * self.V))}
 
     def cache_need(self):
         return StateNeed((self.s_floats,), torch.float32)
@@ -228,9 +229,26 @@ class MatrixMemory(_StateMixer):
         gates = ctx.buffer("matrix_memory.gates", (T, 2 * self.H), torch.float32, dev)
         ops.linear(x, self.p_gates, gates)
         o = ctx.buffer("matrix_memory.o", (T, HV), torch.float32, dev)
-        ops.linear_scan(ops.SCAN_MEMORY, proj[:, :HD], proj[:, HD:2 * HD], proj[:, 2 * HD:2 * HD + HV], gates,
-                        self._bias32, ctx.state, (0, self.n_off, self.m_off), b, o, self.H, self.H, self.D, self.V,
-                        q_scale=self.D ** -0.5, cap=s.gate_cap)
+        q, k, v = proj[:, :HD], proj[:, HD:2 * HD], proj[:, 2 * HD:2 * HD + HV]
+        offsets = (0, self.n_off, self.m_off)
+        pieces = self._pieces(b) if x.dtype != torch.float32 else None
+        if pieces is None:
+            ops.linear_scan(ops.SCAN_MEMORY, q, k, v, gates, self._bias32, ctx.state, offsets, b, o, self.H, self.H,
+                            self.D, self.V, q_scale=self.D ** -0.5, cap=s.gate_cap)
+        else:
+            # long segments in pieces side by side (see Retention.forward); a piece starts from nothing, which for the
+            # running maximum is minus infinity, and also leaves the sum of its log forget gates behind the maxima
+            virtual, seg_first, n_pieces = pieces
+            f_off = self.m_off + self.H
+            held = ctx.buffer("matrix_memory.pieces", (n_pieces, f_off + self.H), torch.float32, dev)
+            held.zero_()
+            held[:, self.m_off:f_off].fill_(float("-inf"))
+            ops.linear_scan(ops.SCAN_MEMORY, q, k, v, gates, self._bias32, held, offsets, virtual, o, self.H, self.H,
+                            self.D, self.V, q_scale=self.D ** -0.5, cap=s.gate_cap, forgot_offset=f_off)
+            ops.memory_pieces_combine(held, ctx.state, offsets, f_off, seg_first, b.seg_slot, _pad8(self.D) * self.V,
+                                      _pad8(self.D), self.H, b.num_segments)
+            ops.linear_scan(ops.SCAN_MEMORY, q, k, v, gates, self._bias32, held, offsets, virtual, o, self.H, self.H,
+                            self.D, self.V, q_scale=self.D ** -0.5, cap=s.gate_cap)
         mixed = ctx.buffer("matrix_memory.mixed", (T, HV), x.dtype, dev)
         ops.head_norm_gate(o, proj[:, 2 * HD + HV:], self.p_norm, 2, 1, s.eps, mixed, self.H, self.V)
         return self._project_out(mixed, ctx)

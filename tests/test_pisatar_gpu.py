@@ -275,11 +275,12 @@ def test_long_decoding(tmp_path_factory, dtype, graph):
 
 
 def test_a_long_prompt_scanned_in_pieces_side_by_side(tmp_path_factory):
-    """On the bfloat16 path a retention cuts a portion of 1,024 tokens or more into pieces that are scanned at the same
-    time, hands the states from piece to piece and scans again.  The outputs of every piece, the state that the tokens
+    """On the bfloat16 path a retention and a matrix memory cut a portion of 1,024 tokens or more into pieces that are
+    scanned at the same time, hand the states from piece to piece and scan again.  The outputs of every piece, the state that the tokens
     decoded afterwards start from, and a short request in the same step must all be right; the decays are slow, so a
     state handed on wrongly would show to the end."""
     raw = config([retention_layer(heads=2, dim=24, vdim=40, rot=16, decay=[0.999, 0.9995]),
+                  parallel_layer(heads=2, kv_heads=1, dim=16, vdim=16, rot=8, mem=(2, 16, 24), scales=(0.3, 1.0), cap=6.0),
                   retention_layer(heads=3, dim=16, vdim=16, rot=8, decay=[0.99, 0.999, 0.9999], ff=0)], width=32)
     entry = model(tmp_path_factory, "pieces", raw)
     reqs = requests_for(entry, (1300, 40), seed=80)
