@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts.base import BuildEnv, CompositeNeed, KVCacheNeed, KVView, LayerContext, StateNeed
+from ..parts.base import BuildEnv, CompositeNeed, KVCacheNeed, KVView, LatentCacheNeed, LayerContext, StateNeed
 from .manager import CacheManager, GroupSpec
 
 
@@ -46,8 +46,10 @@ class CacheStorage:
                 self._composite[key] = tuple(name for name, _ in need.children)
                 for name, child in need.children:
                     register(key + (name,), child)
-            elif isinstance(need, KVCacheNeed):
-                sig = (need.window, need.num_kv_heads, need.head_dim)
+            elif isinstance(need, (KVCacheNeed, LatentCacheNeed)):
+                latent = isinstance(need, LatentCacheNeed)
+                # a latent is one vector a token: stored as "0 heads" of its width, one tensor instead of keys and values
+                sig = (need.window, 0, need.width) if latent else (need.window, need.num_kv_heads, need.head_dim)
                 if sig not in signature_to_group:
                     signature_to_group[sig] = len(self.group_specs)
                     name = "full" if need.window is None else f"window{need.window}"
@@ -55,10 +57,11 @@ class CacheStorage:
                     if need.window is not None and longest_append is not None:
                         per_request = (need.window + longest_append + page_size - 1) // page_size + 1
                         pages = max(1, min(num_pages, max_reside * per_request))
-                    self.group_specs.append(GroupSpec(f"{name}_h{need.num_kv_heads}_d{need.head_dim}",
+                    self.group_specs.append(GroupSpec(f"{name}_latent{need.width}" if latent else
+                                                      f"{name}_h{need.num_kv_heads}_d{need.head_dim}",
                                                       page_size, pages, need.window))
                     self._group_layers.append(0)
-                    self._group_shape.append((need.num_kv_heads, need.head_dim))
+                    self._group_shape.append(sig[1:])
                 g = signature_to_group[sig]
                 self.entry_place[key] = (g, self._group_layers[g])
                 self._group_layers[g] += 1
@@ -92,6 +95,9 @@ class CacheStorage:
             if layers == 0:
                 self.pools.append(None)
                 continue
+            if hkv == 0:                     # latents: [layers, pages, page_size, width]
+                self.pools.append(torch.zeros((layers, spec.num_pages, spec.page_size, d), dtype=dt, device=dev))
+                continue
             self.pools.append(torch.zeros((layers, 2, spec.num_pages, hkv, spec.page_size, d), dtype=dt, device=dev))
         self.states = {i: torch.zeros((self.max_reside + 1,) + tuple(n.shape), dtype=n.dtype, device=dev)
                        for i, n in self._state_needs.items()}
@@ -99,7 +105,7 @@ class CacheStorage:
     def bytes_per_token(self) -> int:
         total = 0
         for layers, (hkv, d) in zip(self._group_layers, self._group_shape):
-            total += layers * 2 * hkv * d * torch.empty((), dtype=self.env.act_dtype).element_size()
+            total += layers * (2 * hkv if hkv else 1) * d * torch.empty((), dtype=self.env.act_dtype).element_size()
         return total
 
     def poison(self) -> None:
@@ -124,7 +130,8 @@ class CacheStorage:
             views = self._layer_views.get(place)
             if views is None:                # the views of a layer's keys and values are made once
                 pool = self.pools[g]
-                views = self._layer_views[place] = (pool[layer, 0], pool[layer, 1])
+                views = self._layer_views[place] = ((pool[layer], None) if self._group_shape[g][0] == 0 else
+                                                    (pool[layer, 0], pool[layer, 1]))
             ctx.kv = KVView(k=views[0], v=views[1], block_table=batch.block_tables[g],
                             page_size=self.group_specs[g].page_size)
         if key in self.states:

@@ -87,6 +87,12 @@ def _register_builtin() -> None:
         name="Pisatar", model_type="pisatar", config_cls=PisatarConfig,
         decoder_spec=pisatar.decoder_spec, weight_sources=pisatar.weight_sources,
         ignorable_tensors=pisatar.ignorable_tensors, checkpoint_shapes=pisatar.checkpoint_shapes))
+    from ..models import gonozen
+    from .gonozen_config import GonozenConfig
+    register_architecture(Architecture(
+        name="Gonozen", model_type="gonozen", config_cls=GonozenConfig,
+        decoder_spec=gonozen.decoder_spec, weight_sources=gonozen.weight_sources,
+        ignorable_tensors=gonozen.ignorable_tensors, checkpoint_shapes=gonozen.checkpoint_shapes))
 
 
 _register_builtin()

@@ -227,29 +227,35 @@ RB_EXPORT int rb_add_rmsnorm(float* stream, const void* delta, const int* rows, 
 // The stand-alone form of the norm, used for kernel tests and by parts that need no residual.
 template <typename TA>
 __global__ void rmsnorm_rows_kernel(const TA* __restrict__ x, const void* __restrict__ w, int w_dtype,
-                                    float eps, float offset, TA* __restrict__ y, int rows, int N) {
+                                    float eps, float offset, TA* __restrict__ y, int rows, int N, int ldx, int ldy) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= rows) return;
-    const TA* xr = x + (size_t)warp * N;
+    const TA* xr = x + (size_t)warp * ldx;
     float ss = 0.f;
     for (int i = lane; i < N; i += 32) { float v = to_f32(xr[i]); ss += v * v; }
     ss = warp_sum(ss);
     const float rstd = 1.0f / sqrtf(ss / (float)N + eps);
-    TA* yr = y + (size_t)warp * N;
+    TA* yr = y + (size_t)warp * ldy;
     for (int i = lane; i < N; i += 32)
         yr[i] = from_f32<TA>(to_f32(xr[i]) * rstd * (offset + load_as_f32(w, w_dtype, i)));
 }
 
-RB_EXPORT int rb_rmsnorm_rows(const void* x, const void* w, int w_dtype, float eps, float offset, void* y,
-                              int act_dtype, int rows, int N, cudaStream_t st) {
+// rows of length N that lie ldx (ldy) elements apart: a run of columns of a wider buffer
+RB_EXPORT int rb_rmsnorm_rows_ld(const void* x, int ldx, const void* w, int w_dtype, float eps, float offset, void* y, int ldy,
+                                 int act_dtype, int rows, int N, cudaStream_t st) {
     if (rows <= 0) return 0;
     const int threads = 128, per_block = threads / 32;
     const int blocks = (rows + per_block - 1) / per_block;
     if (act_dtype == RB_F32)
-        rmsnorm_rows_kernel<float><<<blocks, threads, 0, st>>>((const float*)x, w, w_dtype, eps, offset, (float*)y, rows, N);
+        rmsnorm_rows_kernel<float><<<blocks, threads, 0, st>>>((const float*)x, w, w_dtype, eps, offset, (float*)y, rows, N, ldx, ldy);
     else
-        rmsnorm_rows_kernel<bf16><<<blocks, threads, 0, st>>>((const bf16*)x, w, w_dtype, eps, offset, (bf16*)y, rows, N);
+        rmsnorm_rows_kernel<bf16><<<blocks, threads, 0, st>>>((const bf16*)x, w, w_dtype, eps, offset, (bf16*)y, rows, N, ldx, ldy);
     return rb_launch_status();
+}
+
+RB_EXPORT int rb_rmsnorm_rows(const void* x, const void* w, int w_dtype, float eps, float offset, void* y,
+                              int act_dtype, int rows, int N, cudaStream_t st) {
+    return rb_rmsnorm_rows_ld(x, N, w, w_dtype, eps, offset, y, N, act_dtype, rows, N, st);
 }
 
 // ---------------------------------------------------------------- SwiGLU
@@ -327,3 +333,74 @@ RB_EXPORT int rb_swiglu(const void* gu, void* out, int act_dtype, int T, int I, 
     return rb_launch_status();
 }
 
+
+// ---------------------------------------------------------------- a sublayer's output normed before it joins the stream
+// For layers that norm a sublayer's output as well as its input: stream[r] += rmsnorm(delta[r]) * (offset_post + w_post),
+// and, if asked, out[r] = rmsnorm(stream[r]) * (offset_next + w_next) for the sublayer that runs next: one kernel at
+// every joint of such a layer.  float32 arithmetic; the row stays in shared memory between the two sums.
+template <typename TA>
+__global__ void postnorm_add_norm_kernel(float* __restrict__ stream, const TA* __restrict__ delta, const void* __restrict__ w_post,
+                                         int wp_dtype, float eps_post, float offset_post, const void* __restrict__ w_next,
+                                         int wn_dtype, float eps_next, float offset_next, TA* __restrict__ out, int H) {
+    extern __shared__ float smem[];
+    float* xrow = smem;          // H floats
+    float* scratch = smem + H;   // 33 floats
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    float* s = stream + (size_t)row * H;
+    const TA* d = delta + (size_t)row * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_f32(d[i]);
+        xrow[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd_d = 1.0f / sqrtf(ss / (float)H + eps_post);
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float x = s[i] + xrow[i] * rstd_d * (offset_post + load_as_f32(w_post, wp_dtype, i));
+        s[i] = x;
+        xrow[i] = x;
+        ss2 += x * x;
+    }
+    pdl_trigger_late();
+    if (out == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float rstd = 1.0f / sqrtf(ss2 / (float)H + eps_next);
+    TA* o = out + (size_t)row * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        o[i] = from_f32<TA>(xrow[i] * rstd * (offset_next + load_as_f32(w_next, wn_dtype, i)));
+}
+
+RB_EXPORT int rb_postnorm_add_norm(float* stream, const void* delta, const void* w_post, int wp_dtype, float eps_post,
+                                   float offset_post, const void* w_next, int wn_dtype, float eps_next, float offset_next,
+                                   void* out, int act_dtype, int n_rows, int H, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    int threads = 128;
+    while (threads < 1024 && threads * 8 < H) threads <<= 1;
+    if (act_dtype == RB_F32)
+        return rb_launch_pdl(postnorm_add_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, st, stream, (const float*)delta,
+                             w_post, wp_dtype, eps_post, offset_post, w_next, wn_dtype, eps_next, offset_next, (float*)out, H);
+    return rb_launch_pdl(postnorm_add_norm_kernel<bf16>, dim3(n_rows), dim3(threads), smem, st, stream, (const bf16*)delta, w_post,
+                         wp_dtype, eps_post, offset_post, w_next, wn_dtype, eps_next, offset_next, (bf16*)out, H);
+}
+
+// ---------------------------------------------------------------- soft cap of the logits
+// x <- cap * tanh(x / cap), in place, float32.
+__global__ void softcap_kernel(float* __restrict__ x, float cap, long long total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const float inv = 1.0f / cap;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
+}
+
+RB_EXPORT int rb_softcap(float* x, float cap, long long total, cudaStream_t st) {
+    if (total <= 0) return 0;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    return rb_launch_pdl(softcap_kernel, dim3(blocks), dim3(256), 0, st, x, cap, total);
+}

@@ -1,0 +1,291 @@
+// Attention over a paged cache of latents: every token leaves one vector [rank + rot] in the cache (a normed
+// latent of `rank` numbers, then a rotated key part of `rot` numbers that all heads share), and the heads' keys
+// and values are linear maps of the latent.  The maps are folded into the query and the output: with
+// k_h = U_h c and v_h = V_h c,
+//     q_h . k_h = (U_h^T q_h) . c        and        sum_j a_j v_h(j) = V_h (sum_j a_j c_j),
+// so a head scores the cached latents with a query of `rank` numbers (plus the rotated part against the shared
+// rotated key) and averages the latents themselves; one cached vector serves every head, as key and as value.
+//
+// Kernels: the write of a step's latents (norm, rotation, page write, rotation of the queries' rotated parts),
+// the attention itself on the CUDA cores for any sizes and element types (float32 path, and the plain twin of
+// the tensor-core kernels), and the packing of the per-head values into rows for the output projection.
+#include "common.cuh"
+
+#define LAT_MAX_RANK 1024
+
+// ---------------------------------------------------------------- write of a step's latents
+// One CTA a token.  x: the token's row of the in-projection; the latent's raw numbers at column c_off (rank of
+// them, normed here with weight w), the shared key part behind them (rot numbers, rotated here; element i pairs
+// with i + rot/2).  Both go to the page of the token's position: pool [pages, page_size, rank + rot].
+// The rotated parts of the queries (q at column q_off of xq, heads of [dim | rot]) are rotated into
+// q_rot [heads, T, rot].  cos, sin: float32 [positions, rot/2].
+template <typename TA>
+__global__ void latent_write_kernel(const TA* __restrict__ x, int ldx, int c_off, const void* __restrict__ w, int w_dtype,
+                                    float eps, int rank, int rot, const float* __restrict__ cosT,
+                                    const float* __restrict__ sinT, const int* __restrict__ pos,
+                                    const int* __restrict__ tok_seg, const int* __restrict__ block_table, int bt_stride,
+                                    int page_size, TA* __restrict__ pool, int write_cache, const TA* __restrict__ xq,
+                                    int ldq, int q_off, int heads, int dim, TA* __restrict__ q_rot, int T) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int p = pos[t];
+    const int half = rot >> 1;
+    const float* cr = cosT + (size_t)p * half;
+    const float* sr = sinT + (size_t)p * half;
+    if (write_cache) {
+        const TA* src = x + (size_t)t * ldx + c_off;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+            const float v = to_f32(src[i]);
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        const float rstd = 1.0f / sqrtf(ss / (float)rank + eps);
+        const int page = block_table[(size_t)tok_seg[t] * bt_stride + p / page_size];
+        if (page >= 0) {
+            TA* dst = pool + ((size_t)page * page_size + (p % page_size)) * (size_t)(rank + rot);
+            for (int i = threadIdx.x; i < rank; i += blockDim.x)
+                dst[i] = from_f32<TA>(to_f32(src[i]) * rstd * load_as_f32(w, w_dtype, i));
+            for (int i = threadIdx.x; i < half; i += blockDim.x) {
+                const float u = to_f32(src[rank + i]), v = to_f32(src[rank + half + i]);
+                dst[rank + i] = from_f32<TA>(u * cr[i] - v * sr[i]);
+                dst[rank + half + i] = from_f32<TA>(v * cr[i] + u * sr[i]);
+            }
+        }
+    }
+    if (rot > 0 && q_rot != nullptr) {
+        for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
+            const int h = e / half, i = e % half;
+            const TA* qh = xq + (size_t)t * ldq + q_off + (size_t)h * (dim + rot) + dim;
+            const float u = to_f32(qh[i]), v = to_f32(qh[half + i]);
+            TA* dst = q_rot + ((size_t)h * T + t) * rot;
+            dst[i] = from_f32<TA>(u * cr[i] - v * sr[i]);
+            dst[half + i] = from_f32<TA>(v * cr[i] + u * sr[i]);
+        }
+    }
+}
+
+RB_EXPORT int rb_latent_write(const void* x, int ldx, int c_off, const void* w, int w_dtype, float eps, int rank, int rot,
+                              const float* cosT, const float* sinT, const int* pos, const int* tok_seg,
+                              const int* block_table, int bt_stride, int page_size, void* pool, int write_cache,
+                              const void* xq, int ldq, int q_off, int heads, int dim, void* q_rot, int act_dtype, int T,
+                              cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (rot & 1) return (int)cudaErrorInvalidValue;
+    const int threads = rank >= 512 ? 256 : 128;
+    if (act_dtype == RB_F32)
+        return rb_launch_pdl(latent_write_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)x, ldx, c_off, w, w_dtype,
+                             eps, rank, rot, cosT, sinT, pos, tok_seg, block_table, bt_stride, page_size, (float*)pool,
+                             write_cache, (const float*)xq, ldq, q_off, heads, dim, (float*)q_rot, T);
+    return rb_launch_pdl(latent_write_kernel<bf16>, dim3(T), dim3(threads), 0, st, (const bf16*)x, ldx, c_off, w, w_dtype, eps,
+                         rank, rot, cosT, sinT, pos, tok_seg, block_table, bt_stride, page_size, (bf16*)pool, write_cache,
+                         (const bf16*)xq, ldq, q_off, heads, dim, (bf16*)q_rot, T);
+}
+
+// ---------------------------------------------------------------- attention on the CUDA cores
+// One warp owns one (token, head).  Keys are taken in tiles of 32 aligned to absolute positions, lane j of a tile
+// scores key j against the whole cached vector, and the online softmax (float32) advances tile by tile; the
+// accumulator over the latent's `rank` numbers is spread over the lanes.  A row looks at nothing but its own keys
+// and the tiles are fixed by position, so a token's result does not depend on how the prompt was cut or on what
+// else is in the batch.  q_lat [heads, T, rank], q_rot [heads, T, rot], out [heads, T, rank].
+// A key at position j is visible to the query at p iff lo <= j <= p, lo = max(0, p - window + 1) for window > 0.
+// sink (float32 [heads] or null): a term exp(sink_h) in the denominator that has no key and no value.
+template <typename TA>
+__global__ void __launch_bounds__(128)
+latent_attention_simt_kernel(const TA* __restrict__ q_lat, const TA* __restrict__ q_rot, const TA* __restrict__ pool,
+                             const int* __restrict__ pos, const int* __restrict__ tok_seg,
+                             const int* __restrict__ block_table, int bt_stride, int page_size,
+                             const float* __restrict__ sink, TA* __restrict__ out, int T, int heads, int rank, int rot,
+                             float scale, int window) {
+    extern __shared__ float qs_all[];                    // 4 warps x (rank + rot) floats
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.y * 4 + warp;
+    if (h >= heads) return;                              // no block-wide barrier below
+    const int W = rank + rot;
+    const int p = pos[t];
+    const int* bt = block_table + (size_t)tok_seg[t] * bt_stride;
+    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    float* qs = qs_all + warp * W;
+    const TA* ql = q_lat + ((size_t)h * T + t) * rank;
+    for (int d = lane; d < rank; d += 32) qs[d] = to_f32(ql[d]);
+    if (rot > 0) {
+        const TA* qr = q_rot + ((size_t)h * T + t) * rot;
+        for (int d = lane; d < rot; d += 32) qs[rank + d] = to_f32(qr[d]);
+    }
+    __syncwarp();
+
+    float m = -INFINITY, l = 0.f;
+    float acc[LAT_MAX_RANK / 32];
+#pragma unroll
+    for (int i = 0; i < LAT_MAX_RANK / 32; ++i) acc[i] = 0.f;
+
+    for (int j0 = (lo / 32) * 32; j0 <= p; j0 += 32) {
+        const int j = j0 + lane;
+        const bool valid = j >= lo && j <= p;
+        float s = -INFINITY;
+        if (valid) {
+            const int page = bt[j / page_size];
+            if (page < 0) {
+                s = __int_as_float(0x7fc00000);          // a page that was given back: show it as NaN
+            } else {
+                const TA* kr = pool + ((size_t)page * page_size + (j % page_size)) * (size_t)W;
+                float dot = 0.f;
+                for (int d = 0; d < W; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
+                s = dot * scale;
+            }
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float pj = valid ? expf(s - m_new) : 0.f;
+        const float alpha = expf(m - m_new);             // m = -inf on the first tile gives 0
+        l = l * alpha + warp_sum(pj);
+#pragma unroll
+        for (int i = 0; i < LAT_MAX_RANK / 32; ++i) acc[i] *= alpha;
+        const int jend = min(32, p - j0 + 1);
+        for (int jj = max(0, lo - j0); jj < jend; ++jj) {
+            const float pjj = __shfl_sync(0xffffffffu, pj, jj);
+            const int jk = j0 + jj;
+            const int page = bt[jk / page_size];
+            if (page < 0) continue;
+            const TA* vr = pool + ((size_t)page * page_size + (jk % page_size)) * (size_t)W;
+#pragma unroll
+            for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
+                const int d = lane + 32 * i;
+                if (d < rank) acc[i] = fmaf(pjj, to_f32(vr[d]), acc[i]);
+            }
+        }
+        m = m_new;
+    }
+    if (sink != nullptr) {
+        const float sk = sink[h];
+        const float m_new = fmaxf(m, sk);
+        const float alpha = expf(m - m_new);
+        l = l * alpha + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < LAT_MAX_RANK / 32; ++i) acc[i] *= alpha;
+    }
+    TA* orow = out + ((size_t)h * T + t) * rank;
+    const float inv = 1.0f / l;
+#pragma unroll
+    for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < rank) orow[d] = from_f32<TA>(acc[i] * inv);
+    }
+}
+
+RB_EXPORT int rb_latent_attention_simt(const void* q_lat, const void* q_rot, const void* pool, const int* pos,
+                                       const int* tok_seg, const int* block_table, int bt_stride, int page_size,
+                                       const float* sink, void* out, int act_dtype, int T, int heads, int rank, int rot,
+                                       float scale, int window, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (rank <= 0 || rank > LAT_MAX_RANK || heads <= 0) return (int)cudaErrorInvalidValue;
+    dim3 grid(T, (heads + 3) / 4);
+    const size_t smem = (size_t)4 * (rank + rot) * sizeof(float);
+    if (act_dtype == RB_F32)
+        return rb_launch_pdl(latent_attention_simt_kernel<float>, grid, dim3(128), smem, st, (const float*)q_lat,
+                             (const float*)q_rot, (const float*)pool, pos, tok_seg, block_table, bt_stride, page_size, sink,
+                             (float*)out, T, heads, rank, rot, scale, window);
+    return rb_launch_pdl(latent_attention_simt_kernel<bf16>, grid, dim3(128), smem, st, (const bf16*)q_lat, (const bf16*)q_rot,
+                         (const bf16*)pool, pos, tok_seg, block_table, bt_stride, page_size, sink, (bf16*)out, T, heads,
+                         rank, rot, scale, window);
+}
+
+// ---------------------------------------------------------------- per-head values -> rows, with the output gate
+// out[t, h * vdim + e] = v[h, t, e] * (gate ? sigmoid(gate[t * ldg + h]) : 1).  The gate's logistic is float32.
+template <typename TA>
+__global__ void head_pack_gate_kernel(const TA* __restrict__ v, const TA* __restrict__ gate, int ldg, TA* __restrict__ out,
+                                      int T, int heads, int vdim) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) {
+        const int h = e / vdim, i = e % vdim;
+        float val = to_f32(v[((size_t)h * T + t) * vdim + i]);
+        if (gate != nullptr) val *= 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ldg + h])));
+        out[(size_t)t * heads * vdim + e] = from_f32<TA>(val);
+    }
+}
+
+RB_EXPORT int rb_head_pack_gate(const void* v, const void* gate, int ldg, void* out, int act_dtype, int T, int heads,
+                                int vdim, cudaStream_t st) {
+    if (T <= 0) return 0;
+    const int threads = heads * vdim >= 1024 ? 256 : 128;
+    if (act_dtype == RB_F32)
+        return rb_launch_pdl(head_pack_gate_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)v, (const float*)gate,
+                             ldg, (float*)out, T, heads, vdim);
+    return rb_launch_pdl(head_pack_gate_kernel<bf16>, dim3(T), dim3(threads), 0, st, (const bf16*)v, (const bf16*)gate, ldg,
+                         (bf16*)out, T, heads, vdim);
+}
+
+// ---------------------------------------------------------------- float32 products head by head
+// C[b][m, n] = sum_k A[b][m, k] * W[b][n, k] for b < batch, in true float32 (FFMA), every element accumulated over
+// k in ascending order by one thread: the 32-bit path's form of the two folded maps.  Strides in elements.
+#define HB_BM 64
+#define HB_BN 64
+#define HB_BK 16
+
+__global__ void __launch_bounds__(256)
+gemm_f32_heads_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int M, int N, int K,
+                      int lda, int ldw, int ldc, long long sa, long long sw, long long sc) {
+    __shared__ float As[HB_BK][HB_BM + 4];
+    __shared__ float Ws[HB_BK][HB_BN + 4];
+    pdl_launch_dependents();
+    pdl_wait();
+    A += (size_t)blockIdx.z * sa;
+    W += (size_t)blockIdx.z * sw;
+    C += (size_t)blockIdx.z * sc;
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * HB_BM, n0 = blockIdx.x * HB_BN;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += HB_BK) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int e = tid + r * 256;
+            const int row = e >> 4, kk = e & 15;
+            const int k = k0 + kk;
+            const int m = m0 + row, n = n0 + row;
+            As[kk][row] = (m < M && k < K) ? A[(size_t)m * lda + k] : 0.f;
+            Ws[kk][row] = (n < N && k < K) ? W[(size_t)n * ldw + k] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HB_BK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) C[(size_t)m * ldc + n] = acc[i][j];
+        }
+    }
+}
+
+RB_EXPORT int rb_gemm_f32_heads(const float* A, const float* W, float* C, int batch, int M, int N, int K, int lda, int ldw,
+                                int ldc, long long sa, long long sw, long long sc, cudaStream_t st) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    dim3 grid((N + HB_BN - 1) / HB_BN, (M + HB_BM - 1) / HB_BM, batch);
+    return rb_launch_pdl(gemm_f32_heads_kernel, grid, dim3(256), 0, st, A, W, C, M, N, K, lda, ldw, ldc, sa, sw, sc);
+}

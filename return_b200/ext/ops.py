@@ -81,6 +81,8 @@ def core() -> ctypes.CDLL:
         lib.rb_embedding.argtypes = [P, I, P, P, I, I, I, P]
         lib.rb_add_rmsnorm.argtypes = [P, P, P, P, I, F, F, P, I, I, I, P]
         lib.rb_rmsnorm_rows.argtypes = [P, P, I, F, F, P, I, I, I, P]
+        lib.rb_rmsnorm_rows_ld.argtypes = [P, I, P, I, F, F, P, I, I, I, I, P]
+        lib.rb_rmsnorm_rows_ld.restype = c_int
         lib.rb_swiglu.argtypes = [P, P, I, I, I, I, P]
         lib.rb_gemm_f32.argtypes = [P, P, P, I, I, I, I, I, I, P]
         lib.rb_gemm_skinny.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P]
@@ -93,8 +95,11 @@ def core() -> ctypes.CDLL:
         lib.rb_attention_simt.argtypes = [P, I, P, P, P, P, P, I, I, P, I, I, I, I, I, F, I, P]
         lib.rb_sample.argtypes = [P, I, I, I, P, P, P, P, P, P, I, P]
         lib.rb_argmax.argtypes = [P, I, I, I, P, P]
+        lib.rb_postnorm_add_norm.argtypes = [P, P, P, I, F, F, P, I, F, F, P, I, I, I, P]
+        lib.rb_softcap.argtypes = [P, F, ctypes.c_longlong, P]
         for name in ("rb_embedding", "rb_add_rmsnorm", "rb_rmsnorm_rows", "rb_swiglu", "rb_gemm_f32",
-                     "rb_qk_norm_rope_write", "rb_attention_simt", "rb_sample", "rb_argmax"):
+                     "rb_qk_norm_rope_write", "rb_attention_simt", "rb_sample", "rb_argmax", "rb_postnorm_add_norm",
+                     "rb_softcap"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core
@@ -109,6 +114,8 @@ def build_all():
     paths = [build.library_path("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})]
     paths.append(build.library_path("return_tc5", _TC5_SOURCES, _tc5_defines()))
     paths.append(build.library_path("return_recurrent", _RECURRENT_SOURCES, {"RB_PDL_MODE": PDL_MODE}))
+    paths.append(build.library_path("return_latent", _LATENT_SOURCES, {"RB_PDL_MODE": PDL_MODE}))
+    paths.append(build.library_path("return_moe", _MOE_SOURCES, {"RB_PDL_MODE": PDL_MODE}))
     for d in TC5_ATTENTION_HEAD_DIMS:
         paths.append(build.library_path(f"return_attn_tc5_d{d}", ["attention_tc5.cu"], _attn_tc5_defines(d)))
     for d in PREBUILT_HEAD_DIMS:
@@ -155,12 +162,43 @@ def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.T
                                   dtype_code(x.dtype), x.numel() // N, N, _stream()), "rmsnorm_rows")
 
 
+def rmsnorm_columns(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, offset: float = 0.0) -> None:
+    """out = rmsnorm over the last dim of x [T, N], where x and out may be runs of columns of wider buffers (any row
+    stride, unit stride along a row)."""
+    T, N = x.shape
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == x.shape and out.dtype == x.dtype and weight.numel() == N
+    _check(core().rb_rmsnorm_rows_ld(_ptr(x), x.stride(0), _ptr(weight), dtype_code(weight.dtype), eps, offset, _ptr(out),
+                                     out.stride(0), dtype_code(x.dtype), T, N, _stream()), "rmsnorm_columns")
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> None:
     """out = silu(gate) * up.  ``interleave`` 0: gate_up[t] = [gate | up]; 8: blocks of 8 gate then 8 up."""
     T, I2 = gate_up.shape
     assert out.shape == (T, I2 // 2) and gate_up.is_contiguous() and out.is_contiguous()
     assert out.dtype == gate_up.dtype and interleave in (0, 8)
     _check(core().rb_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I2 // 2, interleave, _stream()), "swiglu")
+
+
+def postnorm_add_norm(stream: torch.Tensor, delta: torch.Tensor, post, nxt=None, out: Optional[torch.Tensor] = None) -> None:
+    """stream (float32) += rmsnorm(delta) * (offset + w) with ``post`` = (w, eps, offset); with ``nxt`` = (w, eps, offset)
+    and ``out``, also out = rmsnorm(stream) * (offset + w): the joint between two sublayers of a layer that norms a
+    sublayer's output as well as its input."""
+    T, H = stream.shape
+    assert stream.dtype == torch.float32 and stream.is_contiguous() and delta.shape == stream.shape and delta.is_contiguous()
+    wp, eps_p, off_p = post
+    assert wp.numel() == H
+    wn, eps_n, off_n = nxt if nxt is not None else (None, 0.0, 0.0)
+    if out is not None:
+        assert wn is not None and wn.numel() == H and out.shape == stream.shape and out.is_contiguous() and out.dtype == delta.dtype
+    _check(core().rb_postnorm_add_norm(_ptr(stream), _ptr(delta), _ptr(wp), dtype_code(wp.dtype), eps_p, off_p, _ptr(wn),
+                                       dtype_code(wn.dtype) if wn is not None else F32, eps_n, off_n, _ptr(out),
+                                       dtype_code(delta.dtype), T, H, _stream()), "postnorm_add_norm")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap), in place; float32."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and cap > 0
+    _check(core().rb_softcap(_ptr(x), float(cap), x.numel(), _stream()), "softcap")
 
 
 # ------------------------------------------------------------------------------- matrix products
@@ -931,6 +969,184 @@ def scaled_sum(a, s1: float, b, s2: float, out) -> None:
     assert a.is_contiguous() and b.is_contiguous() and out.is_contiguous()
     _check(recurrent_lib().rb_scaled_sum(_ptr(a), _is_f32(a), s1, _ptr(b), _is_f32(b), s2, _ptr(out), _is_f32(out),
                                          a.numel(), _stream()), "scaled_sum")
+
+
+# ------------------------------------------------------------------------------- attention over cached latents
+
+_latent = None
+_LATENT_SOURCES = ["latent.cu"]
+LATENT_MAX_RANK = 1024           # numbers of a latent that the attention kernels take
+
+
+def latent_lib() -> ctypes.CDLL:
+    """The kernels of the attention over a paged cache of latents (csrc/latent.cu); compiled when a model that has
+    such a mixer is first run."""
+    global _latent
+    if _latent is None:
+        lib = build.load("return_latent", _LATENT_SOURCES, {"RB_PDL_MODE": PDL_MODE})
+        P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
+        lib.rb_latent_write.argtypes = [P, I, I, P, I, F, I, I, P, P, P, P, P, I, I, P, I, P, I, I, I, I, P, I, I, P]
+        lib.rb_latent_attention_simt.argtypes = [P, P, P, P, P, P, I, I, P, P, I, I, I, I, I, F, I, P]
+        lib.rb_head_pack_gate.argtypes = [P, P, I, P, I, I, I, I, P]
+        lib.rb_gemm_f32_heads.argtypes = [P, P, P, I, I, I, I, I, I, I, L, L, L, P]
+        for name in ("rb_latent_write", "rb_latent_attention_simt", "rb_head_pack_gate", "rb_gemm_f32_heads"):
+            getattr(lib, name).restype = c_int
+        _latent = lib
+    return _latent
+
+
+def latent_write(x, c_off: int, norm_w, eps: float, rank: int, rot: int, cos, sin, batch, block_table, page_size: int,
+                 pool, write_cache: bool, xq=None, q_off: int = 0, heads: int = 0, dim: int = 0, q_rot=None) -> None:
+    """Every token's latent into its page: columns [c_off, c_off + rank) of ``x`` normed with ``norm_w``, the ``rot``
+    columns behind them rotated by the position (element i with i + rot/2).  pool: [pages, page_size, rank + rot].
+    With ``q_rot`` [heads, T, rot], also the rotated parts of the queries (heads of [dim | rot] from column q_off of
+    ``xq``) rotated into it."""
+    T = x.shape[0]
+    assert x.stride(1) == 1 and pool.dtype == x.dtype and pool.is_contiguous() and pool.shape[-1] == rank + rot
+    if rot:
+        assert cos.dtype == sin.dtype == torch.float32 and cos.shape[1] * 2 == rot and cos.is_contiguous() and sin.is_contiguous()
+    else:
+        cos = sin = batch.pos          # never read
+    if q_rot is not None:
+        assert xq is not None and xq.stride(1) == 1 and xq.dtype == x.dtype and q_rot.is_contiguous() and q_rot.dtype == x.dtype
+    _check(latent_lib().rb_latent_write(_ptr(x), x.stride(0), c_off, _ptr(norm_w), dtype_code(norm_w.dtype), eps, rank, rot,
+                                        _ptr(cos), _ptr(sin), _ptr(batch.pos), _ptr(batch.tok_seg), _ptr(block_table),
+                                        block_table.stride(0), page_size, _ptr(pool), 1 if write_cache else 0, _ptr(xq),
+                                        xq.stride(0) if xq is not None else 0, q_off, heads, dim, _ptr(q_rot),
+                                        dtype_code(x.dtype), T, _stream()), "latent_write")
+
+
+def latent_attention_simt(q_lat, q_rot, pool, batch, block_table, page_size: int, sink, out, scale: float, window=None) -> None:
+    """Attention of every token of the step over its request's cached latents, on the CUDA cores: q_lat [heads, T, rank]
+    against the first ``rank`` numbers of a cached vector, q_rot [heads, T, rot] (or None) against the rest; out
+    [heads, T, rank] is the weighted mean of the latents.  ``sink``: float32 [heads] or None."""
+    H, T, R = q_lat.shape
+    rot = q_rot.shape[2] if q_rot is not None else 0
+    assert q_lat.is_contiguous() and out.is_contiguous() and out.shape == q_lat.shape and out.dtype == q_lat.dtype
+    assert pool.dtype == q_lat.dtype and pool.shape[-1] == R + rot and pool.is_contiguous()
+    if sink is not None:
+        assert sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous()
+    _check(latent_lib().rb_latent_attention_simt(_ptr(q_lat), _ptr(q_rot), _ptr(pool), _ptr(batch.pos), _ptr(batch.tok_seg),
+                                                 _ptr(block_table), block_table.stride(0), page_size, _ptr(sink), _ptr(out),
+                                                 dtype_code(q_lat.dtype), T, H, R, rot, scale, int(window or 0), _stream()),
+           "latent_attention_simt")
+
+
+def latent_attention(q_lat, q_rot, pool, batch, block_table, page_size: int, sink, out, scale: float, window=None) -> None:
+    """Attention of every token of the step over its request's cached latents (its own included)."""
+    latent_attention_simt(q_lat, q_rot, pool, batch, block_table, page_size, sink, out, scale, window)
+
+
+def head_pack_gate(v, gate, out) -> None:
+    """out[t, h * vdim + e] = v[h, t, e] * sigmoid(gate[t, h]) (gate: a [T, heads] view of unit stride along a row, or
+    None for no gate)."""
+    H, T, Vd = v.shape
+    assert v.is_contiguous() and out.is_contiguous() and out.shape == (T, H * Vd) and out.dtype == v.dtype
+    if gate is not None:
+        assert gate.dtype == v.dtype and gate.stride(1) == 1 and gate.shape == (T, H)
+    _check(latent_lib().rb_head_pack_gate(_ptr(v), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out),
+                                          dtype_code(v.dtype), T, H, Vd, _stream()), "head_pack_gate")
+
+
+def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[h] = x[h] @ w[h]^T for every head: x [heads, T, K] (any strides with unit stride along K), w [heads, N, K],
+    out [heads, T, N].  float32: the engine's own FFMA kernel, every sum in one order.  bfloat16: the library's batched
+    product with float32 accumulation."""
+    Hh, T, K = x.shape
+    N = w.shape[1]
+    assert w.shape == (Hh, N, K) and out.shape == (Hh, T, N) and x.stride(2) == 1 and w.stride(2) == 1 and out.stride(2) == 1
+    if x.dtype == torch.float32:
+        assert w.dtype == out.dtype == torch.float32
+        _check(latent_lib().rb_gemm_f32_heads(_ptr(x), _ptr(w), _ptr(out), Hh, T, N, K, x.stride(1), w.stride(1), out.stride(1),
+                                              x.stride(0), w.stride(0), out.stride(0), _stream()), "gemm_f32_heads")
+        return
+    if not x.is_cuda:
+        raise KernelError("the engine's kernels run on a CUDA device only; got a CPU tensor")
+    torch.bmm(x, w.transpose(1, 2), out=out)
+
+
+# ------------------------------------------------------------------------------- mixture of experts
+
+_moe = None
+_MOE_SOURCES = ["moe.cu"]
+
+
+def moe_lib() -> ctypes.CDLL:
+    """The kernels of a mixture of experts (csrc/moe.cu); compiled when a model that has one is first run."""
+    global _moe
+    if _moe is None:
+        lib = build.load("return_moe", _MOE_SOURCES, {"RB_PDL_MODE": PDL_MODE})
+        P, I, F = c_void_p, c_int, c_float
+        lib.rb_moe_route.argtypes = [P, I, P, P, I, I, I, I, I, F, P]
+        lib.rb_moe_pair_linear.argtypes = [P, I, I, P, P, P, I, I, I, I, I, P]
+        lib.rb_clamped_glu.argtypes = [P, I, P, I, I, I, I, F, F, P]
+        lib.rb_moe_combine.argtypes = [P, P, P, P, P, I, I, I, I, P]
+        for name in ("rb_moe_route", "rb_moe_pair_linear", "rb_clamped_glu", "rb_moe_combine"):
+            getattr(lib, name).restype = c_int
+        _moe = lib
+    return _moe
+
+
+def moe_route(logits, expert_of, weight, top: int, groups: int = 1, keep: int = 1, tiny: float = 1e-20) -> None:
+    """The router's choice per token from float32 logits [T, E]: softmax over all experts; with ``groups`` > 1 only the
+    experts of the ``keep`` groups (equal runs of neighbours) with the largest best score can be chosen; the ``top``
+    largest scores among them, in falling order, into expert_of (int32 [T, top]) with weight = score / (sum + tiny)."""
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert expert_of.dtype == torch.int32 and expert_of.shape == (T, top) and expert_of.is_contiguous()
+    assert weight.dtype == torch.float32 and weight.shape == (T, top) and weight.is_contiguous()
+    _check(moe_lib().rb_moe_route(_ptr(logits), logits.stride(0), _ptr(expert_of), _ptr(weight), T, E, top, groups, keep, tiny,
+                                  _stream()), "moe_route")
+
+
+def moe_pair_linear(x, in_div: int, w, expert_of, out) -> None:
+    """out[i] = x[i // in_div] @ w[expert_of[i]]^T for every (token, chosen expert) pair i; w [E, N, K]."""
+    E, N, K = w.shape
+    pairs = expert_of.numel()
+    assert x.dtype == w.dtype == out.dtype and x.stride(1) == 1 and w.is_contiguous() and out.stride(1) == 1
+    assert x.shape[1] == K and out.shape == (pairs, N) and x.shape[0] * in_div == pairs
+    _check(moe_lib().rb_moe_pair_linear(_ptr(x), x.stride(0), in_div, _ptr(w), _ptr(expert_of), _ptr(out), out.stride(0),
+                                        dtype_code(x.dtype), pairs, N, K, _stream()), "moe_pair_linear")
+
+
+def clamped_glu(gate_up, out, limit: float, alpha: float) -> None:
+    """gate_up [rows, 2F] = [gate | up]: out = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit) and
+    u = clamp(up, -limit, limit)."""
+    rows, F2 = gate_up.shape
+    assert out.shape == (rows, F2 // 2) and out.dtype == gate_up.dtype and gate_up.stride(1) == 1 and out.stride(1) == 1
+    _check(moe_lib().rb_clamped_glu(_ptr(gate_up), gate_up.stride(0), _ptr(out), out.stride(0), dtype_code(out.dtype), rows,
+                                    F2 // 2, float(limit), float(alpha), _stream()), "clamped_glu")
+
+
+def moe_combine(y, weight, shared, out, row_of=None) -> None:
+    """out[t] = sum_k weight[t, k] * y[row of pair t * top + k] (+ shared[t]); sums in float32 in the order of k."""
+    T, top = weight.shape
+    H = out.shape[1]
+    assert y.shape == (T * top, H) and y.is_contiguous() and out.is_contiguous() and out.dtype == y.dtype
+    if shared is not None:
+        assert shared.shape == out.shape and shared.is_contiguous() and shared.dtype == y.dtype
+    _check(moe_lib().rb_moe_combine(_ptr(y), _ptr(row_of), _ptr(weight), _ptr(shared), _ptr(out), dtype_code(y.dtype), T, H, top,
+                                    _stream()), "moe_combine")
+
+
+def moe_experts(x, gate_up, down, expert_of, weight, shared, out, limit: float, alpha: float, ctx=None) -> None:
+    """out[t] = sum_k weight[t, k] * expert_{expert_of[t, k]}(x[t]) (+ shared[t]); gate_up [E, 2F, H], down [E, H, F]."""
+    E, F2, H = gate_up.shape
+    T, top = expert_of.shape
+    pairs = T * top
+
+    def buf(name, shape):
+        if ctx is not None:
+            return ctx.buffer(name, shape, x.dtype, x.device)
+        return torch.empty(shape, dtype=x.dtype, device=x.device)
+
+    gu = buf("moe.pair_gate_up", (pairs, F2))
+    moe_pair_linear(x, top, gate_up, expert_of, gu)
+    act = buf("moe.pair_act", (pairs, F2 // 2))
+    clamped_glu(gu, act, limit, alpha)
+    y = buf("moe.pair_y", (pairs, H))
+    moe_pair_linear(act, 1, down, expert_of, y)
+    moe_combine(y, weight, shared, out)
 
 
 # ------------------------------------------------------------------------------- sampling

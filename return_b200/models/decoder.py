@@ -123,4 +123,6 @@ class DecoderModel:
             hidden = torch.empty((n_want, H), dtype=self.env.act_dtype, device=dev)
             self.final_norm.add_forward(stream, delta, hidden, rows=batch.want_rows)
             ops.linear(hidden, self.lm_head, logits)
+            if self.spec.logit_softcap is not None:
+                ops.softcap(logits, self.spec.logit_softcap)
         return logits

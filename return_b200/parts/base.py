@@ -48,6 +48,14 @@ class KVCacheNeed:
 
 
 @dataclass(frozen=True)
+class LatentCacheNeed:
+    """The mixer wants one paged vector of ``width`` numbers a token (a latent that serves as key and as value for
+    every head): all of them, or a window."""
+    width: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
 class StateNeed:
     """The mixer wants one tensor of fixed shape per request."""
     shape: Tuple[int, ...]
@@ -73,8 +81,8 @@ class Tiling:
 @dataclass
 class KVView:
     """One cache layer as a mixer sees it."""
-    k: torch.Tensor                   # [num_pages, Hkv, page_size, D]
-    v: torch.Tensor
+    k: torch.Tensor                   # [num_pages, Hkv, page_size, D]; for a LatentCacheNeed [num_pages, page_size, width]
+    v: Optional[torch.Tensor]         # None for a LatentCacheNeed
     block_table: torch.Tensor         # int32 [segments of the step, blocks]
     page_size: int
 

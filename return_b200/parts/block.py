@@ -197,3 +197,90 @@ class ParallelBlock(Block):
         if not has_ff:
             return (mixed,)
         return (mixed, self.feed_forward.forward(b, ctx))
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """x += post_a(mixer(pre_a(x))); x += post_b(feed_forward(pre_b(x))): every sublayer is normed on the way in and on
+    the way out.
+
+    One kernel sits at every joint: it norms the sublayer's output, adds it to the float32 stream and norms the stream
+    for the sublayer that runs next (csrc/elementwise.cu, ``postnorm_add_norm``), also across the border to the next
+    block when that block begins with an RMSNorm of the stream (``first_norm``): the normed rows are then left for it
+    under ``sandwich.prenormed`` in the step's scratch.  The block owes the stream nothing when it returns."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.mixer = MIXERS.build(spec.mixer, env)
+        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, env) if spec.feed_forward is not None else None
+        self._children = {"mixer": self.mixer, "mixer_norm": NORMS.build(spec.mixer_norm, env),
+                          "mixer_post_norm": NORMS.build(spec.mixer_post_norm, env)}
+        if self.feed_forward is not None:
+            self._children.update({"feed_forward": self.feed_forward,
+                                   "feed_forward_norm": NORMS.build(spec.feed_forward_norm, env),
+                                   "feed_forward_post_norm": NORMS.build(spec.feed_forward_post_norm, env)})
+        for name, part in self._children.items():
+            if name.endswith("norm") and getattr(part.spec, "kind", None) != "rmsnorm":
+                raise ValueError("the norms of a sandwich block are RMSNorms")
+
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part in self._children.values())
+
+    def params(self):
+        return {f"{child}.{name}": p for child, part in self._children.items()
+                for name, p in part.params().items()}
+
+    def bind(self, tensors):
+        for child, part in self._children.items():
+            prefix = child + "."
+            part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def batch_tilings(self):
+        out = {}
+        for part in self._children.values():
+            out.update(part.batch_tilings())
+        return out
+
+    def graph_variant(self, n_tokens, longest_context):
+        out = {}
+        for part in self._children.values():
+            out.update(part.graph_variant(n_tokens, longest_context))
+        return out
+
+    def first_norm(self):
+        n = self._children["mixer_norm"]
+        return (n.p_weight, n.spec.eps, n.spec.offset, n.spec.size) if hasattr(n, "p_weight") else None
+
+    @staticmethod
+    def _triple(norm):
+        return norm.p_weight, norm.spec.eps, norm.spec.offset
+
+    def forward(self, stream, delta, ctx):
+        T, H = stream.shape
+        dt, dev = self.env.act_dtype, stream.device
+        c = self._children
+        held = getattr(ctx.batch, "scratch", None)
+        pre = held.pop("sandwich.prenormed", None) if held is not None else None
+        if delta is None and pre is not None and pre["position"] == ctx.position:
+            a = pre["rows"]                                     # the block before this one normed the stream for us
+        else:
+            a = ctx.buffer("sandwich.normed_a", (T, H), dt, dev)
+            c["mixer_norm"].add_forward(stream, delta, a)       # stream += delta; a = norm(stream)
+        mixed = self.mixer.forward(a, ctx)
+        last = mixed, c["mixer_post_norm"]
+        if self.feed_forward is not None:
+            b = ctx.buffer("sandwich.normed_b", (T, H), dt, dev)
+            ops.postnorm_add_norm(stream, mixed, self._triple(c["mixer_post_norm"]), self._triple(c["feed_forward_norm"]), b)
+            last = self.feed_forward.forward(b, ctx), c["feed_forward_post_norm"]
+        nxt = ctx.next_block.first_norm() if ctx.next_block is not None and hasattr(ctx.next_block, "first_norm") else None
+        if nxt is not None and nxt[3] == H and held is not None and isinstance(ctx.next_block, SandwichBlock):
+            rows = ctx.buffer("sandwich.normed_a", (T, H), dt, dev)      # this block's own normed input is used up by now
+            ops.postnorm_add_norm(stream, last[0], self._triple(last[1]), (nxt[0], nxt[1], nxt[2]), rows)
+            held["sandwich.prenormed"] = {"rows": rows, "position": ctx.position + 1}
+        else:
+            ops.postnorm_add_norm(stream, last[0], self._triple(last[1]))
+        return None

@@ -92,6 +92,54 @@ class ScaledRotaryEncoding(PositionEncoding):
         return self._tables
 
 
+@POSITION_ENCODINGS.register("rope_ramped")
+class RampedRotaryEncoding(PositionEncoding):
+    """Rotary tables whose frequencies are stretched along a ramp over the pair index, with one factor on cos and sin
+    (``RampedRopeSpec``).  Frequencies and angles are worked out in float64 on the host and rounded once, to the
+    float32 tables the kernels read."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.rotary_dim % 2 or spec.rotary_dim <= 0:
+            raise ValueError(f"rotary_dim={spec.rotary_dim} must be even and positive")
+        self._tables = None
+
+    @staticmethod
+    def frequencies(spec):
+        """(float64 frequencies [rotary_dim / 2], factor on cos and sin)."""
+        dims, theta = spec.rotary_dim, float(spec.theta)
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        f = theta ** (-2.0 * i / dims)
+        if spec.factor is None:
+            return f, 1.0
+        factor = float(spec.factor)
+
+        def index(turns: float) -> float:
+            return dims * math.log(float(spec.original) / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+        lo = max(math.floor(index(float(spec.fast))), 0)
+        hi = min(math.ceil(index(float(spec.slow))), dims - 1)
+        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        return f / factor * ramp + f * (1.0 - ramp), float(spec.magnitude_slope) * math.log(factor) + 1.0
+
+    def rotary_tables(self):
+        """(cos, sin, rotary_dim); cos and sin are float32 [max_positions, rotary_dim/2] on the device, the factor
+        already in them."""
+        if self._tables is None:
+            s = self.spec
+            key = ("ramped", s, str(self.env.device))
+            shared = _TABLES.get(key)
+            if shared is None:
+                f, mag = self.frequencies(s)
+                ang = torch.outer(torch.arange(s.max_positions, dtype=torch.float64), f)
+                shared = _TABLES[key] = ((ang.cos() * mag).float().contiguous().to(self.env.device),
+                                         (ang.sin() * mag).float().contiguous().to(self.env.device), s.rotary_dim)
+            self._tables = shared
+        return self._tables
+
+    tables = rotary_tables
+
+
 def drop_shared_tables() -> None:
     """Forgets the shared tables (models that still hold them keep them alive)."""
     _TABLES.clear()

@@ -47,6 +47,50 @@ class ScaledRopeSpec:
 
 
 @dataclass(frozen=True)
+class RampedRopeSpec:
+    """Half-split rotary encoding of the first ``rotary_dim`` elements whose frequencies are stretched along a ramp over
+    the pair index.  With f_i = theta^(-2i / rotary_dim) and index(n) = rotary_dim ln(original / (2 pi n)) / (2 ln theta),
+    the ramp runs from lo = max(floor(index(fast)), 0) to hi = min(ceil(index(slow)), rotary_dim - 1):
+    r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), and the frequency is f_i / factor * r_i + f_i * (1 - r_i).  cos and
+    sin are multiplied by ``magnitude_slope`` * ln(factor) + 1.  ``factor`` None: plain frequencies, no factor on the
+    tables.  Tables are worked out in float64."""
+    rotary_dim: int
+    theta: float
+    max_positions: int
+    factor: Optional[float] = None
+    original: float = 0.0
+    fast: float = 0.0
+    slow: float = 0.0
+    magnitude_slope: float = 0.1
+    kind: str = "rope_ramped"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are linear maps of one cached latent a token.  Per head: ``key_dim``
+    unrotated query/key elements, ``rot_dim`` rotated ones (the rotated key part is one vector shared by all heads,
+    projected beside the latent and not normed), ``value_dim`` value elements; the latent has ``kv_rank`` numbers and is
+    RMS-normed (plain weight, ``eps``).  The score is (q . k) * ``scale`` over both parts.  Options: ``q_rank`` (queries
+    go through a normed latent of their own), ``window`` (the last n keys, the query's own included), ``sink`` (a learned
+    term per head in the softmax's denominator that has no key and no value), ``gate`` (a head's output times the
+    logistic of a projection of the mixer's input)."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    rot_dim: int
+    value_dim: int
+    kv_rank: int
+    scale: float
+    eps: float
+    q_rank: Optional[int] = None
+    window: Optional[int] = None
+    sink: bool = False
+    gate: bool = False
+    position: Optional[Any] = None        # the encoding of the rotated part (rotary_dim == rot_dim), None if rot_dim == 0
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Causal grouped-query attention over a paged cache."""
     hidden_size: int
@@ -146,6 +190,48 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class ClampedGLUSpec:
+    """down( g * sigmoid(alpha g) * (u + 1) ) with g = min(gate(x), limit), u = clamp(up(x), -limit, limit); dense, no
+    biases."""
+    hidden_size: int
+    intermediate_size: int
+    limit: float
+    alpha: float = 1.702
+    kind: str = "clamped_glu"
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """A mixture of ``num_experts`` feed-forwards of one form (``expert``, a dense feed-forward's specification) of which
+    every token uses ``top``.  Router scores are a softmax over all experts (float32); with ``groups`` > 1 the experts
+    form that many equal groups of neighbours and only those of the ``keep_groups`` groups with the largest best score
+    can be chosen; the chosen scores divided by their sum (+ ``renorm_tiny``) weigh the experts' outputs.  ``shared``:
+    a feed-forward that runs for every token and is added, or None."""
+    hidden_size: int
+    num_experts: int
+    top: int
+    expert: Any
+    groups: int = 1
+    keep_groups: int = 1
+    shared: Any = None
+    renorm_tiny: float = 1e-20
+    kind: str = "moe"
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """x += post_a(mixer(pre_a(x))); x += post_b(feed_forward(pre_b(x))): a norm before and after each sublayer.
+    ``feed_forward`` None: the layer has none (and no norms for it)."""
+    mixer: Any
+    feed_forward: Any
+    mixer_norm: Any
+    mixer_post_norm: Any
+    feed_forward_norm: Any = None
+    feed_forward_post_norm: Any = None
+    kind: str = "sandwich"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """The arrangement of one layer: x += mixer(norm(x)); x += feed_forward(norm(x))."""
     mixer: Any
@@ -172,6 +258,7 @@ class DecoderSpec:
     final_norm: Any
     tie_embeddings: bool
     embedding_norm: Any = None            # a norm applied to the embedded tokens before the first layer
+    logit_softcap: Optional[float] = None  # logits <- cap * tanh(logits / cap)
 
     @staticmethod
     def in_order(n_layers: int) -> Tuple[ScheduleEntry, ...]:
