@@ -155,7 +155,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
                     const bf16* __restrict__ vpool, const int* __restrict__ tiles,
                     const int* __restrict__ cu_q, const int* __restrict__ seg_pos0,
                     const int* __restrict__ block_table, int bt_stride, int page_size,
-                    bf16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window) {
+                    bf16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window,
+                    const float* __restrict__ sink) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
     bf16* sK = sQ + PF_M * D;                 // two stages
@@ -290,6 +291,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
     float l0 = l_run[0], l1 = l_run[1];
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (sink != nullptr) {                    // a term of the denominator that has no key and no value, not scaled
+        const float sk = sink[h] * LOG2E;
+        l0 += exp2f(sk - m_run[0]);
+        l1 += exp2f(sk - m_run[1]);
+    }
     const float inv0 = 1.f / l0, inv1 = 1.f / l1;
     const int r0 = wrow + g, r1 = r0 + 8;
     const size_t ostride = (size_t)Hq * D;
@@ -395,7 +401,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
                    const int* __restrict__ cu_q, const int* __restrict__ seg_kv_len,
                    const int* __restrict__ block_table, int bt_stride, int page_size,
                    float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out,
-                   int Hq, int Hkv, int m_tiles, float scale_log2, int window, int num_splits, FusedRope fr) {
+                   int Hq, int Hkv, int m_tiles, float scale_log2, int window, int num_splits, FusedRope fr,
+                   const float* __restrict__ sink) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                    // 16 x D
     int* sBT = reinterpret_cast<int*>(sQ + 16 * D);                  // the block-table entries this CTA walks
@@ -661,6 +668,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
         }
         const int h = h0 + r;
         if (num_splits == 1) {
+            if (sink != nullptr) lg += exp2f(sink[h] * LOG2E - mg);
             out[(size_t)tok_row * Hq * D + (size_t)h * D + d] = __float2bfloat16_rn(og / lg);
         } else {
             const size_t pidx = ((size_t)blockIdx.x * Hq + h) * num_splits + split;
@@ -679,7 +687,7 @@ constexpr int COMBINE_THREADS = 128;
 __global__ void __launch_bounds__(COMBINE_THREADS)
 attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     const int* __restrict__ dec_segs, const int* __restrict__ cu_q,
-                    bf16* __restrict__ out, int Hq, int num_splits) {
+                    bf16* __restrict__ out, int Hq, int num_splits, const float* __restrict__ sink) {
     __shared__ float s_w[COMBINE_MAX_SPLITS];
     __shared__ float s_red[2][COMBINE_THREADS / 32];
     pdl_launch_dependents();
@@ -732,6 +740,7 @@ attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
             for (int u = 0; u < UNROLL; ++u)
                 if (s0 + u < num_splits) acc[c] += po[c][u] * s_w[s0 + u];
     }
+    if (sink != nullptr) lg += exp2f(sink[h] * LOG2E - mg);
     const float inv = 1.0f / lg;
 #pragma unroll
     for (int c = 0; c < COLS; ++c) {
@@ -747,7 +756,7 @@ RB_EXPORT int rb_attn_head_dim() { return D; }
 RB_EXPORT int rb_attn_prefill(const void* q, int ld, const void* kpool, const void* vpool, const int* tiles,
                               int n_tiles, const int* cu_q, const int* seg_pos0, const int* block_table,
                               int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale,
-                              int window, cudaStream_t st) {
+                              int window, const float* sink, cudaStream_t st) {
     if (n_tiles <= 0) return 0;
     const size_t smem = (size_t)(PF_M + 4 * PF_N) * D * sizeof(bf16) + BT_CAP * sizeof(int);
     static PerDevice configured;
@@ -758,7 +767,7 @@ RB_EXPORT int rb_attn_prefill(const void* q, int ld, const void* kpool, const vo
     dim3 grid(n_tiles, Hq);
     return rb_launch_pdl(attn_prefill_kernel, grid, dim3(128), smem, st, (const bf16*)q, ld, (const bf16*)kpool,
                          (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride, page_size, (bf16*)out,
-                         Hq, Hkv, scale * LOG2E, window);
+                         Hq, Hkv, scale * LOG2E, window, sink);
 }
 
 // Floats of scratch that rb_attn_decode needs: part_o [n_dec, Hq, splits, D], part_ml [n_dec, Hq, splits, 2].
@@ -770,7 +779,7 @@ namespace {
 int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, const int* dec_segs,
                   int n_dec, const int* cu_q, const int* seg_kv_len, const int* block_table,
                   int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
-                  float scale, int window, int num_splits, const FusedRope* fused, cudaStream_t st) {
+                  float scale, int window, int num_splits, const FusedRope* fused, const float* sink, cudaStream_t st) {
     if (n_dec <= 0) return 0;
     if (num_splits < 1 || num_splits > COMBINE_MAX_SPLITS || (num_splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
     const int G = Hq / Hkv, m_tiles = (G + 15) / 16;
@@ -793,24 +802,24 @@ int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, c
     if (fused != nullptr)
         rc = rb_launch_pdl(attn_decode_kernel<true>, grid, dim3(DC_WARPS * 32), smem, st,
             (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
-            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, *fused);
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, *fused, sink);
     else
         rc = rb_launch_pdl(attn_decode_kernel<false>, grid, dim3(DC_WARPS * 32), smem, st,
             (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
-            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, none);
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, none, sink);
     if (rc != 0 || num_splits == 1) return rc;
     dim3 cgrid(n_dec, Hq);
     return rb_launch_pdl(attn_combine_kernel, cgrid, dim3(128), 0, st, (const float*)part_o, (const float*)part_ml,
-                         dec_segs, cu_q, (bf16*)out, Hq, num_splits);
+                         dec_segs, cu_q, (bf16*)out, Hq, num_splits, sink);
 }
 }  // namespace
 
 RB_EXPORT int rb_attn_decode(const void* q, int ld, const void* kpool, const void* vpool, const int* dec_segs,
                              int n_dec, const int* cu_q, const int* seg_kv_len, const int* block_table,
                              int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
-                             float scale, int window, int num_splits, cudaStream_t st) {
+                             float scale, int window, int num_splits, const float* sink, cudaStream_t st) {
     return launch_decode(q, ld, kpool, vpool, dec_segs, n_dec, cu_q, seg_kv_len, block_table, bt_stride, page_size,
-                         scratch, out, Hq, Hkv, scale, window, num_splits, nullptr, st);
+                         scratch, out, Hq, Hkv, scale, window, num_splits, nullptr, sink, st);
 }
 
 // The same for a step of single tokens only, with the q/k norm, the rotation and the cache write of
@@ -827,7 +836,7 @@ RB_EXPORT int rb_attn_decode_fused(const void* qkv, int ld, void* kpool, void* v
     fr.cos_t = cos_t; fr.sin_t = sin_t; fr.rot_dim = rot_dim;
     fr.kpool = (bf16*)kpool; fr.vpool = (bf16*)vpool; fr.write_kv = write_kv;
     return launch_decode(qkv, ld, kpool, vpool, dec_segs, n_dec, cu_q, seg_kv_len, block_table, bt_stride, page_size,
-                         scratch, out, Hq, Hkv, scale, window, num_splits, &fr, st);
+                         scratch, out, Hq, Hkv, scale, window, num_splits, &fr, nullptr, st);
 }
 
 // ------------------------------------------------------------------ decode attention without allocation
@@ -862,5 +871,5 @@ RB_EXPORT int rb_attn_decode_static(const void* q, int ld, const void* kpool, co
         }
     }
     return rb_attn_decode(q, ld, kpool, vpool, dec_segs, n_dec, cu_q, seg_kv_len, block_table, bt_stride, page_size,
-                          scratch_of_device[dev], out, Hq, Hkv, scale, window, num_splits, st);
+                          scratch_of_device[dev], out, Hq, Hkv, scale, window, num_splits, nullptr, st);
 }

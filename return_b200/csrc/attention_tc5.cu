@@ -133,7 +133,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                         const int* __restrict__ block_table, int bt_stride, int page_size,
                         bf16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int total_rows,
-                        int* __restrict__ status) {
+                        int* __restrict__ status, const float* __restrict__ sink) {
     // The swizzled tiles need 1024-byte alignment.  The kernel has no static shared memory, so the
     // dynamic window starts at the CTA's shared base; should it ever not be aligned, the kernel
     // reports it and does nothing.
@@ -330,7 +330,8 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                 }
             }
         } else if (n_mine > 0) {
-            const float inv = 1.f / l_run;
+            // a sink: a term of the denominator that has no key and no value, not scaled
+            const float inv = 1.f / (sink != nullptr ? l_run + exp2f(sink[h] * LOG2E - m_ref) : l_run);
             bf16* orow = out + token * ((size_t)Hq * D) + (size_t)h * D;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
@@ -501,7 +502,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
 __global__ void __launch_bounds__(256)
 merge_key_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                         const int* __restrict__ tiles, const int* __restrict__ cu_q, int n_split, int total_rows,
-                        int Hq, bf16* __restrict__ out) {
+                        int Hq, bf16* __restrict__ out, const float* __restrict__ sink) {
     const int seg = tiles[2 * blockIdx.y], row0 = tiles[2 * blockIdx.y + 1];
     const int q_begin = cu_q[seg];
     const int m_rows = min(NQ * QM, cu_q[seg + 1] - q_begin - row0);
@@ -522,6 +523,7 @@ merge_key_splits_kernel(const float* __restrict__ part_o, const float* __restric
 #pragma unroll
         for (int i = 0; i < PER; ++i) acc[i] += prow[i] * wgt;
     }
+    if (sink != nullptr) l_all += exp2f(sink[h] * LOG2E - m_all);
     const float inv = 1.f / l_all;
     bf16* orow = out + token * ((size_t)Hq * D) + (size_t)h * D + lane * PER;
 #pragma unroll
@@ -545,7 +547,8 @@ RB_EXPORT long long rb_attn_tc5_split_floats(int n_split, int total_rows, int Hq
 RB_EXPORT int rb_attn_prefill_tc5(const void* q, int ld, const void* kpool, const void* vpool, const int* tiles,
                                   int n_tiles, const int* cu_q, const int* seg_pos0, const int* block_table,
                                   int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale, int window,
-                                  int n_split, void* scratch, int total_rows, int* status, cudaStream_t st) {
+                                  int n_split, void* scratch, int total_rows, int* status, const float* sink,
+                                  cudaStream_t st) {
     if (n_tiles <= 0) return 0;
     if (n_tiles > 65535 || n_split < 1 || n_split > 64 || (n_split > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
     static PerDevice configured;
@@ -558,10 +561,10 @@ RB_EXPORT int rb_attn_prefill_tc5(const void* q, int ld, const void* kpool, cons
     dim3 grid(Hq, n_tiles, n_split);
     attn_prefill_tc5_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(
         (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride,
-        page_size, (bf16*)out, Hq, Hkv, scale * LOG2E, window, part_o, part_ml, total_rows, status);
+        page_size, (bf16*)out, Hq, Hkv, scale * LOG2E, window, part_o, part_ml, total_rows, status, sink);
     if (n_split > 1) {
         dim3 mgrid(Hq, n_tiles, NQ * QM / 8);
-        merge_key_splits_kernel<<<mgrid, 256, 0, st>>>(part_o, part_ml, tiles, cu_q, n_split, total_rows, Hq, (bf16*)out);
+        merge_key_splits_kernel<<<mgrid, 256, 0, st>>>(part_o, part_ml, tiles, cu_q, n_split, total_rows, Hq, (bf16*)out, sink);
     }
     return rb_launch_status();
 }

@@ -8,7 +8,8 @@
 //
 // Kernels: the write of a step's latents (norm, rotation, page write, rotation of the queries' rotated parts),
 // the attention itself on the CUDA cores for any sizes and element types (float32 path, and the plain twin of
-// the tensor-core kernels), and the packing of the per-head values into rows for the output projection.
+// the tensor-core kernels, which are the engine's paged attention kernels run with one shared key/value head whose
+// keys and values are both the cached vector), the heads' output gate, and the float32 products head by head.
 #include "common.cuh"
 
 #define LAT_MAX_RANK 1024
@@ -16,16 +17,19 @@
 // ---------------------------------------------------------------- write of a step's latents
 // One CTA a token.  x: the token's row of the in-projection; the latent's raw numbers at column c_off (rank of
 // them, normed here with weight w), the shared key part behind them (rot numbers, rotated here; element i pairs
-// with i + rot/2).  Both go to the page of the token's position: pool [pages, page_size, rank + rot].
-// The rotated parts of the queries (q at column q_off of xq, heads of [dim | rot]) are rotated into
-// q_rot [heads, T, rot].  cos, sin: float32 [positions, rot/2].
+// with i + rot/2).  Both go to the page of the token's position: pool [pages, page_size, width], width >= rank + rot
+// (a multiple of 16 for the tensor-core kernels; the columns behind rank + rot are written as zeros).
+// The rotated parts of the queries (q at column q_off of xq, heads of [dim | rot]) are rotated into the query rows
+// that the attention reads, q_abs [T, heads, width], at columns [rank, rank + rot) of a head; the columns behind are
+// zeroed; the first `rank` columns are another kernel's.  cos, sin: float32 [positions, rot/2].
 template <typename TA>
 __global__ void latent_write_kernel(const TA* __restrict__ x, int ldx, int c_off, const void* __restrict__ w, int w_dtype,
                                     float eps, int rank, int rot, const float* __restrict__ cosT,
                                     const float* __restrict__ sinT, const int* __restrict__ pos,
                                     const int* __restrict__ tok_seg, const int* __restrict__ block_table, int bt_stride,
-                                    int page_size, TA* __restrict__ pool, int write_cache, const TA* __restrict__ xq,
-                                    int ldq, int q_off, int heads, int dim, TA* __restrict__ q_rot, int T) {
+                                    int page_size, TA* __restrict__ pool, int width, int write_cache,
+                                    const TA* __restrict__ xq, int ldq, int q_off, int heads, int dim,
+                                    TA* __restrict__ q_abs) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -45,7 +49,7 @@ __global__ void latent_write_kernel(const TA* __restrict__ x, int ldx, int c_off
         const float rstd = 1.0f / sqrtf(ss / (float)rank + eps);
         const int page = block_table[(size_t)tok_seg[t] * bt_stride + p / page_size];
         if (page >= 0) {
-            TA* dst = pool + ((size_t)page * page_size + (p % page_size)) * (size_t)(rank + rot);
+            TA* dst = pool + ((size_t)page * page_size + (p % page_size)) * (size_t)width;
             for (int i = threadIdx.x; i < rank; i += blockDim.x)
                 dst[i] = from_f32<TA>(to_f32(src[i]) * rstd * load_as_f32(w, w_dtype, i));
             for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -53,35 +57,40 @@ __global__ void latent_write_kernel(const TA* __restrict__ x, int ldx, int c_off
                 dst[rank + i] = from_f32<TA>(u * cr[i] - v * sr[i]);
                 dst[rank + half + i] = from_f32<TA>(v * cr[i] + u * sr[i]);
             }
+            for (int i = rank + rot + threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<TA>(0.f);
         }
     }
-    if (rot > 0 && q_rot != nullptr) {
+    if (q_abs != nullptr) {
+        TA* qa = q_abs + (size_t)t * heads * width;
         for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
             const int h = e / half, i = e % half;
             const TA* qh = xq + (size_t)t * ldq + q_off + (size_t)h * (dim + rot) + dim;
             const float u = to_f32(qh[i]), v = to_f32(qh[half + i]);
-            TA* dst = q_rot + ((size_t)h * T + t) * rot;
+            TA* dst = qa + (size_t)h * width + rank;
             dst[i] = from_f32<TA>(u * cr[i] - v * sr[i]);
             dst[half + i] = from_f32<TA>(v * cr[i] + u * sr[i]);
         }
+        const int pad = width - rank - rot;
+        for (int e = threadIdx.x; e < heads * pad; e += blockDim.x)
+            qa[(size_t)(e / pad) * width + rank + rot + e % pad] = from_f32<TA>(0.f);
     }
 }
 
 RB_EXPORT int rb_latent_write(const void* x, int ldx, int c_off, const void* w, int w_dtype, float eps, int rank, int rot,
                               const float* cosT, const float* sinT, const int* pos, const int* tok_seg,
-                              const int* block_table, int bt_stride, int page_size, void* pool, int write_cache,
-                              const void* xq, int ldq, int q_off, int heads, int dim, void* q_rot, int act_dtype, int T,
+                              const int* block_table, int bt_stride, int page_size, void* pool, int width, int write_cache,
+                              const void* xq, int ldq, int q_off, int heads, int dim, void* q_abs, int act_dtype, int T,
                               cudaStream_t st) {
     if (T <= 0) return 0;
-    if (rot & 1) return (int)cudaErrorInvalidValue;
+    if ((rot & 1) || width < rank + rot) return (int)cudaErrorInvalidValue;
     const int threads = rank >= 512 ? 256 : 128;
     if (act_dtype == RB_F32)
         return rb_launch_pdl(latent_write_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)x, ldx, c_off, w, w_dtype,
-                             eps, rank, rot, cosT, sinT, pos, tok_seg, block_table, bt_stride, page_size, (float*)pool,
-                             write_cache, (const float*)xq, ldq, q_off, heads, dim, (float*)q_rot, T);
+                             eps, rank, rot, cosT, sinT, pos, tok_seg, block_table, bt_stride, page_size, (float*)pool, width,
+                             write_cache, (const float*)xq, ldq, q_off, heads, dim, (float*)q_abs);
     return rb_launch_pdl(latent_write_kernel<bf16>, dim3(T), dim3(threads), 0, st, (const bf16*)x, ldx, c_off, w, w_dtype, eps,
-                         rank, rot, cosT, sinT, pos, tok_seg, block_table, bt_stride, page_size, (bf16*)pool, write_cache,
-                         (const bf16*)xq, ldq, q_off, heads, dim, (bf16*)q_rot, T);
+                         rank, rot, cosT, sinT, pos, tok_seg, block_table, bt_stride, page_size, (bf16*)pool, width, write_cache,
+                         (const bf16*)xq, ldq, q_off, heads, dim, (bf16*)q_abs);
 }
 
 // ---------------------------------------------------------------- attention on the CUDA cores
@@ -89,15 +98,16 @@ RB_EXPORT int rb_latent_write(const void* x, int ldx, int c_off, const void* w, 
 // scores key j against the whole cached vector, and the online softmax (float32) advances tile by tile; the
 // accumulator over the latent's `rank` numbers is spread over the lanes.  A row looks at nothing but its own keys
 // and the tiles are fixed by position, so a token's result does not depend on how the prompt was cut or on what
-// else is in the batch.  q_lat [heads, T, rank], q_rot [heads, T, rot], out [heads, T, rank].
+// else is in the batch.  q_abs [T, heads, width] (a head's query in the latent's space, then its rotated part),
+// out [T, heads, width] (the first `rank` columns of a head are written).
 // A key at position j is visible to the query at p iff lo <= j <= p, lo = max(0, p - window + 1) for window > 0.
 // sink (float32 [heads] or null): a term exp(sink_h) in the denominator that has no key and no value.
 template <typename TA>
 __global__ void __launch_bounds__(128)
-latent_attention_simt_kernel(const TA* __restrict__ q_lat, const TA* __restrict__ q_rot, const TA* __restrict__ pool,
+latent_attention_simt_kernel(const TA* __restrict__ q_abs, const TA* __restrict__ pool,
                              const int* __restrict__ pos, const int* __restrict__ tok_seg,
                              const int* __restrict__ block_table, int bt_stride, int page_size,
-                             const float* __restrict__ sink, TA* __restrict__ out, int T, int heads, int rank, int rot,
+                             const float* __restrict__ sink, TA* __restrict__ out, int heads, int rank, int rot, int width,
                              float scale, int window) {
     extern __shared__ float qs_all[];                    // 4 warps x (rank + rot) floats
     pdl_launch_dependents();
@@ -111,12 +121,8 @@ latent_attention_simt_kernel(const TA* __restrict__ q_lat, const TA* __restrict_
     const int* bt = block_table + (size_t)tok_seg[t] * bt_stride;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     float* qs = qs_all + warp * W;
-    const TA* ql = q_lat + ((size_t)h * T + t) * rank;
-    for (int d = lane; d < rank; d += 32) qs[d] = to_f32(ql[d]);
-    if (rot > 0) {
-        const TA* qr = q_rot + ((size_t)h * T + t) * rot;
-        for (int d = lane; d < rot; d += 32) qs[rank + d] = to_f32(qr[d]);
-    }
+    const TA* ql = q_abs + ((size_t)t * heads + h) * width;
+    for (int d = lane; d < W; d += 32) qs[d] = to_f32(ql[d]);
     __syncwarp();
 
     float m = -INFINITY, l = 0.f;
@@ -133,7 +139,7 @@ latent_attention_simt_kernel(const TA* __restrict__ q_lat, const TA* __restrict_
             if (page < 0) {
                 s = __int_as_float(0x7fc00000);          // a page that was given back: show it as NaN
             } else {
-                const TA* kr = pool + ((size_t)page * page_size + (j % page_size)) * (size_t)W;
+                const TA* kr = pool + ((size_t)page * page_size + (j % page_size)) * (size_t)width;
                 float dot = 0.f;
                 for (int d = 0; d < W; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
                 s = dot * scale;
@@ -151,7 +157,7 @@ latent_attention_simt_kernel(const TA* __restrict__ q_lat, const TA* __restrict_
             const int jk = j0 + jj;
             const int page = bt[jk / page_size];
             if (page < 0) continue;
-            const TA* vr = pool + ((size_t)page * page_size + (jk % page_size)) * (size_t)W;
+            const TA* vr = pool + ((size_t)page * page_size + (jk % page_size)) * (size_t)width;
 #pragma unroll
             for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
                 const int d = lane + 32 * i;
@@ -168,7 +174,7 @@ latent_attention_simt_kernel(const TA* __restrict__ q_lat, const TA* __restrict_
 #pragma unroll
         for (int i = 0; i < LAT_MAX_RANK / 32; ++i) acc[i] *= alpha;
     }
-    TA* orow = out + ((size_t)h * T + t) * rank;
+    TA* orow = out + ((size_t)t * heads + h) * width;
     const float inv = 1.0f / l;
 #pragma unroll
     for (int i = 0; i < LAT_MAX_RANK / 32; ++i) {
@@ -177,48 +183,43 @@ latent_attention_simt_kernel(const TA* __restrict__ q_lat, const TA* __restrict_
     }
 }
 
-RB_EXPORT int rb_latent_attention_simt(const void* q_lat, const void* q_rot, const void* pool, const int* pos,
+RB_EXPORT int rb_latent_attention_simt(const void* q_abs, const void* pool, const int* pos,
                                        const int* tok_seg, const int* block_table, int bt_stride, int page_size,
                                        const float* sink, void* out, int act_dtype, int T, int heads, int rank, int rot,
-                                       float scale, int window, cudaStream_t st) {
+                                       int width, float scale, int window, cudaStream_t st) {
     if (T <= 0) return 0;
-    if (rank <= 0 || rank > LAT_MAX_RANK || heads <= 0) return (int)cudaErrorInvalidValue;
+    if (rank <= 0 || rank > LAT_MAX_RANK || heads <= 0 || width < rank + rot) return (int)cudaErrorInvalidValue;
     dim3 grid(T, (heads + 3) / 4);
     const size_t smem = (size_t)4 * (rank + rot) * sizeof(float);
     if (act_dtype == RB_F32)
-        return rb_launch_pdl(latent_attention_simt_kernel<float>, grid, dim3(128), smem, st, (const float*)q_lat,
-                             (const float*)q_rot, (const float*)pool, pos, tok_seg, block_table, bt_stride, page_size, sink,
-                             (float*)out, T, heads, rank, rot, scale, window);
-    return rb_launch_pdl(latent_attention_simt_kernel<bf16>, grid, dim3(128), smem, st, (const bf16*)q_lat, (const bf16*)q_rot,
-                         (const bf16*)pool, pos, tok_seg, block_table, bt_stride, page_size, sink, (bf16*)out, T, heads,
-                         rank, rot, scale, window);
+        return rb_launch_pdl(latent_attention_simt_kernel<float>, grid, dim3(128), smem, st, (const float*)q_abs,
+                             (const float*)pool, pos, tok_seg, block_table, bt_stride, page_size, sink,
+                             (float*)out, heads, rank, rot, width, scale, window);
+    return rb_launch_pdl(latent_attention_simt_kernel<bf16>, grid, dim3(128), smem, st, (const bf16*)q_abs,
+                         (const bf16*)pool, pos, tok_seg, block_table, bt_stride, page_size, sink, (bf16*)out, heads,
+                         rank, rot, width, scale, window);
 }
 
-// ---------------------------------------------------------------- per-head values -> rows, with the output gate
-// out[t, h * vdim + e] = v[h, t, e] * (gate ? sigmoid(gate[t * ldg + h]) : 1).  The gate's logistic is float32.
+// ---------------------------------------------------------------- the output gate of the heads
+// x[t, h * vdim + e] *= sigmoid(gate[t * ldg + h]), in place.  The gate's logistic is float32.
 template <typename TA>
-__global__ void head_pack_gate_kernel(const TA* __restrict__ v, const TA* __restrict__ gate, int ldg, TA* __restrict__ out,
-                                      int T, int heads, int vdim) {
+__global__ void head_gate_kernel(TA* __restrict__ x, const TA* __restrict__ gate, int ldg, int heads, int vdim) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) {
-        const int h = e / vdim, i = e % vdim;
-        float val = to_f32(v[((size_t)h * T + t) * vdim + i]);
-        if (gate != nullptr) val *= 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ldg + h])));
-        out[(size_t)t * heads * vdim + e] = from_f32<TA>(val);
+        const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ldg + e / vdim])));
+        TA* p = x + (size_t)t * heads * vdim + e;
+        *p = from_f32<TA>(to_f32(*p) * g);
     }
 }
 
-RB_EXPORT int rb_head_pack_gate(const void* v, const void* gate, int ldg, void* out, int act_dtype, int T, int heads,
-                                int vdim, cudaStream_t st) {
+RB_EXPORT int rb_head_gate(void* x, const void* gate, int ldg, int act_dtype, int T, int heads, int vdim, cudaStream_t st) {
     if (T <= 0) return 0;
     const int threads = heads * vdim >= 1024 ? 256 : 128;
     if (act_dtype == RB_F32)
-        return rb_launch_pdl(head_pack_gate_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)v, (const float*)gate,
-                             ldg, (float*)out, T, heads, vdim);
-    return rb_launch_pdl(head_pack_gate_kernel<bf16>, dim3(T), dim3(threads), 0, st, (const bf16*)v, (const bf16*)gate, ldg,
-                         (bf16*)out, T, heads, vdim);
+        return rb_launch_pdl(head_gate_kernel<float>, dim3(T), dim3(threads), 0, st, (float*)x, (const float*)gate, ldg, heads, vdim);
+    return rb_launch_pdl(head_gate_kernel<bf16>, dim3(T), dim3(threads), 0, st, (bf16*)x, (const bf16*)gate, ldg, heads, vdim);
 }
 
 // ---------------------------------------------------------------- float32 products head by head

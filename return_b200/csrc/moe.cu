@@ -199,3 +199,178 @@ RB_EXPORT int rb_moe_combine(const void* y, const int* row_of, const float* weig
     return rb_launch_pdl(moe_combine_kernel<bf16>, dim3(T), dim3(threads), 0, st, (const bf16*)y, row_of, weight,
                          (const bf16*)shared, (bf16*)out, H, top);
 }
+
+// ---------------------------------------------------------------- the pairs in the order of their experts
+// A counting sort by one CTA: offsets[e] .. offsets[e + 1] is expert e's run of places, pair_at[place] the pair that
+// stands there, place_of[pair] its inverse.  Which of an expert's pairs gets which place is left to the atomics: every
+// row of the products below is worked out by itself, so the places change no result.
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ expert_of, int pairs, int E, int* __restrict__ offsets, int* __restrict__ pair_at,
+                int* __restrict__ place_of) {
+    extern __shared__ int sort_smem[];                    // E counts, then E cursors
+    int* counts = sort_smem;
+    int* cursor = sort_smem + E;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&counts[expert_of[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = run;
+            cursor[e] = run;
+            run += counts[e];
+        }
+        offsets[E] = run;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int place = atomicAdd(&cursor[expert_of[i]], 1);
+        pair_at[place] = i;
+        place_of[i] = place;
+    }
+}
+
+RB_EXPORT int rb_moe_sort(const int* expert_of, int pairs, int E, int* offsets, int* pair_at, int* place_of, cudaStream_t st) {
+    if (pairs <= 0) return 0;
+    const size_t smem = (size_t)2 * E * sizeof(int);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    return rb_launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), smem, st, expert_of, pairs, E, offsets, pair_at, place_of);
+}
+
+// ---------------------------------------------------------------- the experts' products on the tensor cores
+// C[place, n] = sum_k A[row(place), k] * W[e][n, k] for every place of expert e's run, bfloat16 in, float32
+// accumulation (mma.sync m16n8k16), bfloat16 out.  row(place) = pair_at[place] / in_div when pair_at is given (the
+// first product reads the tokens' rows where they lie), else the place itself (the second reads what the first left).
+// A CTA owns a tile of 64 places of one expert x 128 output columns; it finds its expert by walking the offsets,
+// and leaves at once if the step has fewer tiles than the grid (which is sized for the worst case, so that nothing
+// about a launch depends on the router's choice).  Operands come in through a three-stage cp.async pipeline; rows
+// behind an expert's run and columns behind K are filled with zeros.  K % 8 == 0; rows 16-byte aligned.
+#define GG_BM 64
+#define GG_BN 128
+#define GG_BK 32
+#define GG_LD 40                                           // padded row of a tile in shared memory (elements)
+#define GG_STAGES 3
+
+__device__ __forceinline__ void gg_cp16(void* smem, const void* gmem, bool pred) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = pred ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void gg_ldsm4(unsigned (&r)[4], const void* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void gg_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(256)
+moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ pair_at, int in_div,
+                        const bf16* __restrict__ W, const int* __restrict__ offsets, int E, bf16* __restrict__ C, int ldc,
+                        int N, int K) {
+    __shared__ __align__(16) bf16 sA[GG_STAGES][GG_BM * GG_LD];
+    __shared__ __align__(16) bf16 sB[GG_STAGES][GG_BN * GG_LD];
+    __shared__ int s_tile[3];                             // expert, first place of the tile, places in it
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        int left = blockIdx.x, e = 0, found = -1, first = 0, count = 0;
+        for (; e < E; ++e) {
+            const int lo = offsets[e], n = offsets[e + 1] - lo;
+            const int tiles = (n + GG_BM - 1) / GG_BM;
+            if (left < tiles) { found = e; first = lo + left * GG_BM; count = min(GG_BM, n - left * GG_BM); break; }
+            left -= tiles;
+        }
+        s_tile[0] = found; s_tile[1] = first; s_tile[2] = count;
+    }
+    __syncthreads();
+    const int e = s_tile[0];
+    if (e < 0) return;
+    const int first = s_tile[1], rows = s_tile[2];
+    const int n0 = blockIdx.y * GG_BN;
+    const bf16* We = W + (size_t)e * N * K;
+
+    // what this thread copies every stage: one 16-byte piece of A, two of B
+    const int a_row = tid >> 2, a_ch = tid & 3;
+    const bool a_ok = a_row < rows;
+    const int a_place = first + a_row;
+    const size_t a_src = a_ok ? (size_t)(pair_at ? pair_at[a_place] / in_div : a_place) * lda : 0;
+    const int b_row0 = tid >> 2, b_row1 = b_row0 + 64, b_ch = tid & 3;
+    const bool b_ok0 = n0 + b_row0 < N, b_ok1 = n0 + b_row1 < N;
+    const int kt_count = (K + GG_BK - 1) / GG_BK;
+    auto load_stage = [&](int stage, int kt) {
+        const int k = kt * GG_BK + a_ch * 8;
+        const bool kin = k < K;
+        gg_cp16(&sA[stage][a_row * GG_LD + a_ch * 8], A + a_src + (kin ? k : 0), a_ok && kin);
+        gg_cp16(&sB[stage][b_row0 * GG_LD + b_ch * 8], We + (size_t)(b_ok0 ? n0 + b_row0 : 0) * K + (kin ? k : 0), b_ok0 && kin);
+        gg_cp16(&sB[stage][b_row1 * GG_LD + b_ch * 8], We + (size_t)(b_ok1 ? n0 + b_row1 : 0) * K + (kin ? k : 0), b_ok1 && kin);
+    };
+    for (int s = 0; s < GG_STAGES - 1; ++s) {
+        if (s < kt_count) load_stage(s, s);
+        asm volatile("cp.async.commit_group;\n" ::);
+    }
+    const int wm = (warp >> 2) * 32, wn = (warp & 3) * 32;   // the warp's 32 x 32 part of the tile
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+
+    for (int kt = 0; kt < kt_count; ++kt) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(GG_STAGES - 2));
+        __syncthreads();                                  // stage kt has landed; everyone is done with stage kt - 1
+        if (kt + GG_STAGES - 1 < kt_count) load_stage((kt + GG_STAGES - 1) % GG_STAGES, kt + GG_STAGES - 1);
+        asm volatile("cp.async.commit_group;\n" ::);
+        const bf16* tA = sA[kt % GG_STAGES];
+        const bf16* tB = sB[kt % GG_STAGES];
+#pragma unroll
+        for (int ks = 0; ks < GG_BK / 16; ++ks) {
+            unsigned af[2][4], bfr[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                gg_ldsm4(af[i], tA + (wm + i * 16 + (lane & 15)) * GG_LD + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                gg_ldsm4(bfr[j], tB + (wn + j * 16 + (lane & 7) + ((lane >> 4) << 3)) * GG_LD + ks * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    gg_mma(acc[i][2 * j], af[i], bfr[j][0], bfr[j][1]);
+                    gg_mma(acc[i][2 * j + 1], af[i], bfr[j][2], bfr[j][3]);
+                }
+        }
+    }
+    pdl_trigger_late();
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm + i * 16 + g + half * 8;
+            if (r >= rows) continue;
+            bf16* crow = C + (size_t)(first + r) * ldc;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = n0 + wn + j * 8 + 2 * t4;
+                if (n < N) crow[n] = __float2bfloat16_rn(acc[i][j][half * 2]);
+                if (n + 1 < N) crow[n + 1] = __float2bfloat16_rn(acc[i][j][half * 2 + 1]);
+            }
+        }
+}
+
+RB_EXPORT int rb_moe_grouped_gemm(const void* A, int lda, const int* pair_at, int in_div, const void* W, const int* offsets,
+                                  int E, void* C, int ldc, int places, int N, int K, cudaStream_t st) {
+    if (places <= 0 || N <= 0) return 0;
+    if (K % 8 || lda % 8 || ((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return (int)cudaErrorInvalidValue;
+    dim3 grid((places + GG_BM - 1) / GG_BM + E, (N + GG_BN - 1) / GG_BN);
+    return rb_launch_pdl(moe_grouped_gemm_kernel, grid, dim3(256), 0, st, (const bf16*)A, lda, pair_at, in_div, (const bf16*)W,
+                         offsets, E, (bf16*)C, ldc, N, K);
+}

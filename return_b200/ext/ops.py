@@ -523,8 +523,8 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
             raise KernelError(f"head_dim={head_dim}: the attention kernels take multiples of 16 from 16 to 256")
         lib = build.load(f"return_attn_d{head_dim}", ["attention_mma.cu"], _attn_defines(head_dim))
         P, I, F = c_void_p, c_int, c_float
-        lib.rb_attn_prefill.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, P]
-        lib.rb_attn_decode.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P]
+        lib.rb_attn_prefill.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, P, P]
+        lib.rb_attn_decode.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P, P]
         lib.rb_attn_decode_fused.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P, P, I, F, F, P, P, I, I, P]
         lib.rb_attn_decode_fused.restype = c_int
         lib.rb_attn_decode_scratch_floats.argtypes = [I, I, I]
@@ -567,7 +567,7 @@ def attention_tc5_lib(head_dim: int) -> ctypes.CDLL:
             raise KernelError(f"head_dim={head_dim}: the tcgen05 attention kernel takes {TC5_ATTENTION_HEAD_DIMS}")
         lib = build.load(f"return_attn_tc5_d{head_dim}", ["attention_tc5.cu"], _attn_tc5_defines(head_dim))
         P, I, F = c_void_p, c_int, c_float
-        lib.rb_attn_prefill_tc5.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, I, P, I, P, P]
+        lib.rb_attn_prefill_tc5.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, I, P, I, P, P, P]
         lib.rb_attn_tc5_split_floats.argtypes = [I, I, I]
         lib.rb_attn_tc5_split_floats.restype = ctypes.c_longlong
         lib.rb_attn_prefill_tc5.restype = c_int
@@ -575,8 +575,15 @@ def attention_tc5_lib(head_dim: int) -> ctypes.CDLL:
     return lib
 
 
+def _sink_ptr(sink, num_heads):
+    if sink is None:
+        return None
+    assert sink.dtype == torch.float32 and sink.numel() == num_heads and sink.is_contiguous()
+    return _ptr(sink)
+
+
 def attention_prefill_tc5(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_table, page_size, out, num_heads,
-                          num_kv_heads, head_dim, scale, window=0, num_splits=1, held=None) -> None:
+                          num_kv_heads, head_dim, scale, window=0, num_splits=1, held=None, sink=None) -> None:
     """tcgen05 attention for the listed (segment, first row) blocks of up to TC5_TILE_ROWS query rows
     (the blocks with the longest contexts should come first: they take longest).  ``num_splits`` > 1 splits
     every block's keys over that many CTAs and merges them in a second launch; ``held``: the step's map of
@@ -598,7 +605,7 @@ def attention_prefill_tc5(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_tabl
                                    tiles.shape[0], _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table),
                                    block_table.stride(0), page_size, _ptr(out), num_heads, num_kv_heads, scale,
                                    int(window or 0), num_splits, _ptr(scratch), T, _ptr(tc5_status(qkv.device)),
-                                   _stream()), "attention_prefill_tc5", 2 if num_splits > 1 else 1)
+                                   _sink_ptr(sink, num_heads), _stream()), "attention_prefill_tc5", 2 if num_splits > 1 else 1)
 
 
 PREFILL_SPLIT_MIN_KEYS = 512       # a CTA of a split block keeps at least this many keys
@@ -645,15 +652,15 @@ def decode_splits(n_ctas_base: int, max_kv_len: int, ctas_per_sm: int = 2) -> in
 
 
 def attention_prefill_mma(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_table, page_size, out, num_heads,
-                          num_kv_heads, head_dim, scale, window=0) -> None:
+                          num_kv_heads, head_dim, scale, window=0, sink=None) -> None:
     """Tensor-core attention for the listed (segment, first row) tiles of up to 64 query rows."""
     assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
     assert tiles.dtype == torch.int32 and tiles.is_contiguous()
     lib = attention_lib(head_dim)
     _check(lib.rb_attn_prefill(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(tiles), tiles.shape[0],
                                _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table), block_table.stride(0), page_size,
-                               _ptr(out), num_heads, num_kv_heads, scale, int(window or 0), _stream()),
-           "attention_prefill")
+                               _ptr(out), num_heads, num_kv_heads, scale, int(window or 0), _sink_ptr(sink, num_heads),
+                               _stream()), "attention_prefill")
 
 
 def _split_scratch(lib, n, num_heads, num_splits, device, held=None):
@@ -670,7 +677,7 @@ def _split_scratch(lib, n, num_heads, num_splits, device, held=None):
 
 
 def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, block_table, page_size, out,
-                         num_heads, num_kv_heads, head_dim, scale, window=0, num_splits=1, held=None) -> None:
+                         num_heads, num_kv_heads, head_dim, scale, window=0, num_splits=1, held=None, sink=None) -> None:
     """Tensor-core attention for segments of one token, the keys split ``num_splits`` ways."""
     assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
     lib = attention_lib(head_dim)
@@ -679,7 +686,7 @@ def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, blo
     _check(lib.rb_attn_decode(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(decode_segs), n,
                               _ptr(cu_q), _ptr(seg_kv_len), _ptr(block_table), block_table.stride(0), page_size,
                               _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale, int(window or 0),
-                              num_splits, _stream()), "attention_decode", 2 if num_splits > 1 else 1)
+                              num_splits, _sink_ptr(sink, num_heads), _stream()), "attention_decode", 2 if num_splits > 1 else 1)
 
 
 def _decode_split_count(batch, num_heads, num_kv_heads, window) -> int:
@@ -758,13 +765,15 @@ def attention_decode_fused(qkv, q_weight, k_weight, eps, offset, cos, sin, rot_d
 
 
 def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num_heads, num_kv_heads,
-                    head_dim, scale, window=None) -> None:
+                    head_dim, scale, window=None, sink=None) -> None:
     """Attention of every token of the step over its request's cached keys (its own included).
 
     float32: the CUDA-core kernel, whose result does not depend on how the work was cut.
     bfloat16: the tensor-core kernels, one for prompt portions and one (split over the keys) for
     single decoded tokens."""
     if qkv.dtype == torch.float32:
+        if sink is not None:
+            raise KernelError("the float32 attention kernel takes no sink")
         attention_simt(qkv, k_pool, v_pool, batch.pos, batch.tok_seg, block_table, page_size, out,
                        num_heads, num_kv_heads, head_dim, scale, window or 0)
         return
@@ -773,15 +782,15 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
         if head_dim in TC5_ATTENTION_HEAD_DIMS:
             attention_prefill_tc5(qkv, k_pool, v_pool, batch.tiles[TILES_TC5], batch.cu_q, batch.seg_pos0, block_table,
                                   page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
-                                  _prefill_split_count(batch, num_heads, window), getattr(batch, "scratch", None))
+                                  _prefill_split_count(batch, num_heads, window), getattr(batch, "scratch", None), sink)
         else:
             attention_prefill_mma(qkv, k_pool, v_pool, batch.tiles[TILES_MMA], batch.cu_q, batch.seg_pos0, block_table,
-                                  page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0)
+                                  page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0, sink)
     n_dec = host.decode_segs.shape[0]
     if n_dec:
         attention_decode_mma(qkv, k_pool, v_pool, batch.decode_segs, batch.cu_q, batch.seg_kv_len, block_table,
                              page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
-                             _decode_split_count(batch, num_heads, num_kv_heads, window), getattr(batch, "scratch", None))
+                             _decode_split_count(batch, num_heads, num_kv_heads, window), getattr(batch, "scratch", None), sink)
 
 
 # ------------------------------------------------------------------------------- mixers with a matrix state
@@ -985,67 +994,86 @@ def latent_lib() -> ctypes.CDLL:
     if _latent is None:
         lib = build.load("return_latent", _LATENT_SOURCES, {"RB_PDL_MODE": PDL_MODE})
         P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
-        lib.rb_latent_write.argtypes = [P, I, I, P, I, F, I, I, P, P, P, P, P, I, I, P, I, P, I, I, I, I, P, I, I, P]
-        lib.rb_latent_attention_simt.argtypes = [P, P, P, P, P, P, I, I, P, P, I, I, I, I, I, F, I, P]
-        lib.rb_head_pack_gate.argtypes = [P, P, I, P, I, I, I, I, P]
+        lib.rb_latent_write.argtypes = [P, I, I, P, I, F, I, I, P, P, P, P, P, I, I, P, I, I, P, I, I, I, I, P, I, I, P]
+        lib.rb_latent_attention_simt.argtypes = [P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, P]
+        lib.rb_head_gate.argtypes = [P, P, I, I, I, I, I, P]
         lib.rb_gemm_f32_heads.argtypes = [P, P, P, I, I, I, I, I, I, I, L, L, L, P]
-        for name in ("rb_latent_write", "rb_latent_attention_simt", "rb_head_pack_gate", "rb_gemm_f32_heads"):
+        for name in ("rb_latent_write", "rb_latent_attention_simt", "rb_head_gate", "rb_gemm_f32_heads"):
             getattr(lib, name).restype = c_int
         _latent = lib
     return _latent
 
 
 def latent_write(x, c_off: int, norm_w, eps: float, rank: int, rot: int, cos, sin, batch, block_table, page_size: int,
-                 pool, write_cache: bool, xq=None, q_off: int = 0, heads: int = 0, dim: int = 0, q_rot=None) -> None:
+                 pool, write_cache: bool, xq, q_off: int, heads: int, dim: int, q_abs) -> None:
     """Every token's latent into its page: columns [c_off, c_off + rank) of ``x`` normed with ``norm_w``, the ``rot``
-    columns behind them rotated by the position (element i with i + rot/2).  pool: [pages, page_size, rank + rot].
-    With ``q_rot`` [heads, T, rot], also the rotated parts of the queries (heads of [dim | rot] from column q_off of
-    ``xq``) rotated into it."""
+    columns behind them rotated by the position (element i with i + rot/2), zeros up to the pool's width.
+    pool: [pages, page_size, width].  Also the rotated parts of the queries (heads of [dim | rot] from column q_off of
+    ``xq``) rotated into columns [rank, rank + rot) of every head of q_abs [T, heads * width], zeros behind them."""
     T = x.shape[0]
-    assert x.stride(1) == 1 and pool.dtype == x.dtype and pool.is_contiguous() and pool.shape[-1] == rank + rot
+    width = pool.shape[-1]
+    assert x.stride(1) == 1 and pool.dtype == x.dtype and pool.is_contiguous() and width >= rank + rot
+    assert q_abs.is_contiguous() and q_abs.dtype == x.dtype and q_abs.shape == (T, heads * width)
     if rot:
         assert cos.dtype == sin.dtype == torch.float32 and cos.shape[1] * 2 == rot and cos.is_contiguous() and sin.is_contiguous()
+        assert xq.stride(1) == 1 and xq.dtype == x.dtype
     else:
         cos = sin = batch.pos          # never read
-    if q_rot is not None:
-        assert xq is not None and xq.stride(1) == 1 and xq.dtype == x.dtype and q_rot.is_contiguous() and q_rot.dtype == x.dtype
     _check(latent_lib().rb_latent_write(_ptr(x), x.stride(0), c_off, _ptr(norm_w), dtype_code(norm_w.dtype), eps, rank, rot,
                                         _ptr(cos), _ptr(sin), _ptr(batch.pos), _ptr(batch.tok_seg), _ptr(block_table),
-                                        block_table.stride(0), page_size, _ptr(pool), 1 if write_cache else 0, _ptr(xq),
-                                        xq.stride(0) if xq is not None else 0, q_off, heads, dim, _ptr(q_rot),
-                                        dtype_code(x.dtype), T, _stream()), "latent_write")
+                                        block_table.stride(0), page_size, _ptr(pool), width, 1 if write_cache else 0, _ptr(xq),
+                                        xq.stride(0), q_off, heads, dim, _ptr(q_abs), dtype_code(x.dtype), T, _stream()),
+           "latent_write")
 
 
-def latent_attention_simt(q_lat, q_rot, pool, batch, block_table, page_size: int, sink, out, scale: float, window=None) -> None:
-    """Attention of every token of the step over its request's cached latents, on the CUDA cores: q_lat [heads, T, rank]
-    against the first ``rank`` numbers of a cached vector, q_rot [heads, T, rot] (or None) against the rest; out
-    [heads, T, rank] is the weighted mean of the latents.  ``sink``: float32 [heads] or None."""
-    H, T, R = q_lat.shape
-    rot = q_rot.shape[2] if q_rot is not None else 0
-    assert q_lat.is_contiguous() and out.is_contiguous() and out.shape == q_lat.shape and out.dtype == q_lat.dtype
-    assert pool.dtype == q_lat.dtype and pool.shape[-1] == R + rot and pool.is_contiguous()
+def latent_attention_simt(q_abs, pool, batch, block_table, page_size: int, sink, out, heads: int, rank: int, rot: int,
+                          scale: float, window=None) -> None:
+    """Attention of every token of the step over its request's cached latents, on the CUDA cores: a head's query
+    q_abs[t, h] (``rank`` numbers in the latent's space, then ``rot`` rotated ones) against the cached vectors; the first
+    ``rank`` columns of out[t, h] get the weighted mean of the latents.  ``sink``: float32 [heads] or None."""
+    T = q_abs.shape[0]
+    width = pool.shape[-1]
+    assert q_abs.is_contiguous() and out.is_contiguous() and out.shape == q_abs.shape == (T, heads * width) and out.dtype == q_abs.dtype
+    assert pool.dtype == q_abs.dtype and pool.is_contiguous()
     if sink is not None:
-        assert sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous()
-    _check(latent_lib().rb_latent_attention_simt(_ptr(q_lat), _ptr(q_rot), _ptr(pool), _ptr(batch.pos), _ptr(batch.tok_seg),
+        assert sink.dtype == torch.float32 and sink.numel() == heads and sink.is_contiguous()
+    _check(latent_lib().rb_latent_attention_simt(_ptr(q_abs), _ptr(pool), _ptr(batch.pos), _ptr(batch.tok_seg),
                                                  _ptr(block_table), block_table.stride(0), page_size, _ptr(sink), _ptr(out),
-                                                 dtype_code(q_lat.dtype), T, H, R, rot, scale, int(window or 0), _stream()),
-           "latent_attention_simt")
+                                                 dtype_code(q_abs.dtype), T, heads, rank, rot, width, scale, int(window or 0),
+                                                 _stream()), "latent_attention_simt")
 
 
-def latent_attention(q_lat, q_rot, pool, batch, block_table, page_size: int, sink, out, scale: float, window=None) -> None:
-    """Attention of every token of the step over its request's cached latents (its own included)."""
-    latent_attention_simt(q_lat, q_rot, pool, batch, block_table, page_size, sink, out, scale, window)
+LATENT_TC_MAX_WIDTH = 256        # widest cached vector that the tensor-core attention kernels take as a head
 
 
-def head_pack_gate(v, gate, out) -> None:
-    """out[t, h * vdim + e] = v[h, t, e] * sigmoid(gate[t, h]) (gate: a [T, heads] view of unit stride along a row, or
-    None for no gate)."""
-    H, T, Vd = v.shape
-    assert v.is_contiguous() and out.is_contiguous() and out.shape == (T, H * Vd) and out.dtype == v.dtype
-    if gate is not None:
-        assert gate.dtype == v.dtype and gate.stride(1) == 1 and gate.shape == (T, H)
-    _check(latent_lib().rb_head_pack_gate(_ptr(v), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out),
-                                          dtype_code(v.dtype), T, H, Vd, _stream()), "head_pack_gate")
+def latent_on_tensor_cores(dtype, width: int) -> bool:
+    """Whether the attention over latents of this (padded) width runs on the engine's tensor-core attention kernels."""
+    return dtype == torch.bfloat16 and width % 16 == 0 and width <= LATENT_TC_MAX_WIDTH
+
+
+def latent_attention(q_abs, pool, batch, block_table, page_size: int, sink, out, heads: int, rank: int, rot: int,
+                     scale: float, window=None) -> None:
+    """Attention of every token of the step over its request's cached latents (its own included).
+
+    bfloat16 with a cached vector of up to 256 numbers: the engine's paged attention kernels (tcgen05 or mma.sync for
+    prompt portions, split over the keys for decoded tokens) with one key/value head for all query heads, whose keys and
+    values are both the cached vector: a head's output row then holds the weighted mean of the latents in its first
+    ``rank`` columns (and that of the rotated key parts behind them, which nobody reads).  Otherwise, and in float32:
+    the CUDA-core kernel, whose result does not depend on how the work was cut."""
+    width = pool.shape[-1]
+    if latent_on_tensor_cores(q_abs.dtype, width):
+        as_heads = pool.unsqueeze(1)                       # [pages, 1 kv head, page_size, width]
+        paged_attention(q_abs, as_heads, as_heads, batch, block_table, page_size, out, heads, 1, width, scale, window, sink)
+        return
+    latent_attention_simt(q_abs, pool, batch, block_table, page_size, sink, out, heads, rank, rot, scale, window)
+
+
+def head_gate(x, gate, heads: int) -> None:
+    """x[t, h * vdim + e] *= sigmoid(gate[t, h]), in place (gate: a [T, heads] view of unit stride along a row)."""
+    T, HV = x.shape
+    assert x.is_contiguous() and gate.dtype == x.dtype and gate.stride(1) == 1 and gate.shape == (T, heads) and HV % heads == 0
+    _check(latent_lib().rb_head_gate(_ptr(x), _ptr(gate), gate.stride(0), dtype_code(x.dtype), T, heads, HV // heads,
+                                     _stream()), "head_gate")
 
 
 def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -1081,7 +1109,10 @@ def moe_lib() -> ctypes.CDLL:
         lib.rb_moe_pair_linear.argtypes = [P, I, I, P, P, P, I, I, I, I, I, P]
         lib.rb_clamped_glu.argtypes = [P, I, P, I, I, I, I, F, F, P]
         lib.rb_moe_combine.argtypes = [P, P, P, P, P, I, I, I, I, P]
-        for name in ("rb_moe_route", "rb_moe_pair_linear", "rb_clamped_glu", "rb_moe_combine"):
+        lib.rb_moe_sort.argtypes = [P, I, I, P, P, P, P]
+        lib.rb_moe_grouped_gemm.argtypes = [P, I, P, I, P, P, I, P, I, I, I, I, P]
+        for name in ("rb_moe_route", "rb_moe_pair_linear", "rb_clamped_glu", "rb_moe_combine", "rb_moe_sort",
+                     "rb_moe_grouped_gemm"):
             getattr(lib, name).restype = c_int
         _moe = lib
     return _moe
@@ -1129,22 +1160,59 @@ def moe_combine(y, weight, shared, out, row_of=None) -> None:
                                     _stream()), "moe_combine")
 
 
+def moe_sort(expert_of, num_experts: int, offsets, pair_at, place_of) -> None:
+    """The (token, chosen expert) pairs in the order of their experts: offsets int32 [E + 1] (an expert's run of places),
+    pair_at[place] and its inverse place_of[pair], int32 [pairs]."""
+    pairs = expert_of.numel()
+    assert expert_of.dtype == offsets.dtype == pair_at.dtype == place_of.dtype == torch.int32
+    assert offsets.numel() == num_experts + 1 and pair_at.numel() == pairs and place_of.numel() == pairs
+    _check(moe_lib().rb_moe_sort(_ptr(expert_of), pairs, num_experts, _ptr(offsets), _ptr(pair_at), _ptr(place_of), _stream()),
+           "moe_sort")
+
+
+def moe_grouped_gemm(x, pair_at, in_div: int, w, offsets, out) -> None:
+    """out[place] = x[row(place)] @ w[expert of the place]^T on the tensor cores, bfloat16: row(place) = pair_at[place] //
+    in_div, or the place itself with pair_at None.  w [E, N, K]; offsets int32 [E + 1]."""
+    E, N, K = w.shape
+    places = out.shape[0]
+    assert x.dtype == w.dtype == out.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous() and out.stride(1) == 1
+    assert x.shape[1] == K and out.shape[1] == N
+    _check(moe_lib().rb_moe_grouped_gemm(_ptr(x), x.stride(0), _ptr(pair_at), in_div, _ptr(w), _ptr(offsets), E, _ptr(out),
+                                         out.stride(0), places, N, K, _stream()), "moe_grouped_gemm")
+
+
+# From this many (token, expert) pairs on, a step's experts run as tiles on the tensor cores over the pairs sorted by
+# expert; below, every pair streams its expert's weights (a step of decoded tokens: few pairs, most on experts of their own).
+MOE_GROUPED_MIN_PAIRS = 64
+
+
 def moe_experts(x, gate_up, down, expert_of, weight, shared, out, limit: float, alpha: float, ctx=None) -> None:
     """out[t] = sum_k weight[t, k] * expert_{expert_of[t, k]}(x[t]) (+ shared[t]); gate_up [E, 2F, H], down [E, H, F]."""
     E, F2, H = gate_up.shape
     T, top = expert_of.shape
     pairs = T * top
 
-    def buf(name, shape):
+    def buf(name, shape, dtype=None):
         if ctx is not None:
-            return ctx.buffer(name, shape, x.dtype, x.device)
-        return torch.empty(shape, dtype=x.dtype, device=x.device)
+            return ctx.buffer(name, shape, dtype or x.dtype, x.device)
+        return torch.empty(shape, dtype=dtype or x.dtype, device=x.device)
 
     gu = buf("moe.pair_gate_up", (pairs, F2))
-    moe_pair_linear(x, top, gate_up, expert_of, gu)
     act = buf("moe.pair_act", (pairs, F2 // 2))
-    clamped_glu(gu, act, limit, alpha)
     y = buf("moe.pair_y", (pairs, H))
+    if (x.dtype == torch.bfloat16 and pairs >= MOE_GROUPED_MIN_PAIRS and H % 8 == 0 and F2 % 16 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0):
+        offsets = buf("moe.offsets", (E + 1,), torch.int32)
+        pair_at = buf("moe.pair_at", (pairs,), torch.int32)
+        place_of = buf("moe.place_of", (pairs,), torch.int32)
+        moe_sort(expert_of, E, offsets, pair_at, place_of)
+        moe_grouped_gemm(x, pair_at, top, gate_up, offsets, gu)
+        clamped_glu(gu, act, limit, alpha)
+        moe_grouped_gemm(act, None, 1, down, offsets, y)
+        moe_combine(y, weight, shared, out, row_of=place_of)
+        return
+    moe_pair_linear(x, top, gate_up, expert_of, gu)
+    clamped_glu(gu, act, limit, alpha)
     moe_pair_linear(act, 1, down, expert_of, y)
     moe_combine(y, weight, shared, out)
 

@@ -17,7 +17,7 @@ from __future__ import annotations
 import torch
 
 from ..ext import ops
-from .base import MIXERS, POSITION_ENCODINGS, LatentCacheNeed, Mixer, ParamSpec
+from .base import MIXERS, POSITION_ENCODINGS, LatentCacheNeed, Mixer, ParamSpec, Tiling
 
 
 @MIXERS.register("latent_attention")
@@ -40,6 +40,8 @@ class LatentAttention(Mixer):
         self.c_off = self.first
         self.g_off = self.first + s.kv_rank + s.rot_dim
         self.in_size = self.g_off + (s.num_heads if s.gate else 0)
+        # a cached vector's width: latent and rotated part, padded to whole 16s (the tensor-core kernels' head sizes)
+        self.width = (s.kv_rank + s.rot_dim + 15) // 16 * 16
 
     # ------------------------------------------------------------------ parameters and cache
     def params(self):
@@ -65,13 +67,32 @@ class LatentAttention(Mixer):
         self.sink_f32 = self.p_sink.float().contiguous() if s.sink else None
 
     def cache_need(self):
-        return LatentCacheNeed(self.spec.kv_rank + self.spec.rot_dim, self.spec.window)
+        return LatentCacheNeed(self.width, self.spec.window)
+
+    def _on_tensor_cores(self):
+        return ops.latent_on_tensor_cores(self.env.act_dtype, self.width)
+
+    def batch_tilings(self):
+        """The row blocks of the tensor-core attention kernel for prompt portions that this width runs on."""
+        if not self._on_tensor_cores():
+            return {}
+        if self.width in ops.TC5_ATTENTION_HEAD_DIMS:
+            return {ops.TILES_TC5: Tiling(ops.TC5_TILE_ROWS, heaviest_first=True)}
+        return {ops.TILES_MMA: Tiling(ops.MMA_TILE_ROWS)}
+
+    def graph_variant(self, n_tokens, longest_context):
+        """A captured step cannot change the grid of the split-KV decode kernel: the number of key splits is fixed per
+        captured graph (all query heads share the one key/value head)."""
+        if not self._on_tensor_cores():
+            return {}
+        s = self.spec
+        return {ops.decode_splits_key(s.num_heads, 1, s.window): ops.decode_splits_for(n_tokens, longest_context, s.num_heads, 1, s.window)}
 
     # ------------------------------------------------------------------ one step
     def forward(self, x, ctx):
         s, b, kv = self.spec, ctx.batch, ctx.kv
         T, dt, dev = x.shape[0], x.dtype, x.device
-        H, D, R, C = s.num_heads, s.key_dim, s.rot_dim, s.kv_rank
+        H, D, R, C, W = s.num_heads, s.key_dim, s.rot_dim, s.kv_rank, self.width
         proj = ctx.buffer("latent.in", (T, self.in_size), dt, dev)
         ops.linear(x, self.p_in, proj)
         if s.q_rank is not None:
@@ -79,23 +100,22 @@ class LatentAttention(Mixer):
             ops.rmsnorm_columns(proj[:, :s.q_rank], self.p_q_norm_weight, s.eps, cq)
             q = ctx.buffer("latent.q", (T, self.q_size), dt, dev)
             ops.linear(cq, self.p_uq, q)
-            q_off = 0
         else:
-            q, q_off = proj, 0
+            q = proj                                             # the queries are the first columns of the projection
         cos, sin, _ = self.position.rotary_tables() if self.position is not None else (None, None, 0)
-        q_rot = ctx.buffer("latent.q_rot", (H, T, R), dt, dev) if R else None
+        # a head's query as the attention reads it: [its unrotated part carried into the latent's space | its rotated part]
+        q_abs = ctx.buffer("latent.q_abs", (T, H * W), dt, dev)
         ops.latent_write(proj, self.c_off, self.p_kv_norm_weight, s.eps, C, R, cos, sin, b, kv.block_table, kv.page_size,
-                         kv.k, ctx.write_cache, xq=q, q_off=q_off, heads=H, dim=D, q_rot=q_rot)
-        # the unrotated parts of the queries, head by head, into the latent's space
-        q_heads = q[:, q_off:q_off + self.q_size].view(T, H, self.q_head)[:, :, :D].transpose(0, 1)      # [H, T, D]
-        q_lat = ctx.buffer("latent.q_lat", (H, T, C), dt, dev)
-        ops.linear_heads(q_heads, self.uk_t, q_lat)
-        o_lat = ctx.buffer("latent.o_lat", (H, T, C), dt, dev)
-        ops.latent_attention(q_lat, q_rot, kv.k, b, kv.block_table, kv.page_size, self.sink_f32, o_lat, s.scale, s.window)
-        v = ctx.buffer("latent.v", (H, T, s.value_dim), dt, dev)
-        ops.linear_heads(o_lat, self.uv_h, v)
+                         kv.k, ctx.write_cache, q, 0, H, D, q_abs)
+        q_heads = q[:, :self.q_size].view(T, H, self.q_head)[:, :, :D].transpose(0, 1)                   # [H, T, D]
+        ops.linear_heads(q_heads, self.uk_t, q_abs.view(T, H, W)[:, :, :C].transpose(0, 1))
+        o_abs = ctx.buffer("latent.o_abs", (T, H * W), dt, dev)
+        ops.latent_attention(q_abs, kv.k, b, kv.block_table, kv.page_size, self.sink_f32, o_abs, H, C, R, s.scale, s.window)
+        # the weighted means of the latents, head by head, into the heads' value spaces
         packed = ctx.buffer("latent.packed", (T, H * s.value_dim), dt, dev)
-        ops.head_pack_gate(v, proj[:, self.g_off:self.g_off + H] if s.gate else None, packed)
+        ops.linear_heads(o_abs.view(T, H, W)[:, :, :C].transpose(0, 1), self.uv_h, packed.view(T, H, s.value_dim).transpose(0, 1))
+        if s.gate:
+            ops.head_gate(packed, proj[:, self.g_off:self.g_off + H], H)
         y = ctx.buffer("latent.y", (T, s.hidden_size), dt, dev)
         ops.linear(packed, self.p_o, y)
         return y
