@@ -561,3 +561,83 @@ def compare_designs(size: str, tokens: int, batch: int, steps: int, warmup: int,
         del r["prefill_kernels"], r["decode_kernels"]
     return {"size": size, "width": W, "ff": ff, "heads": H, "kv_heads": G, "layers": L, "tokens": tokens, "batch": batch,
             "pisatar": new, "qwen3": old, "kernels": kernels}
+
+
+def gonozen_raw_config(width: int, ff: int, heads: int, layers: int, vocab: int, window: int = 1024) -> dict:
+    """A Gonozen configuration at the layer sizes of a Qwen3 model of this width: heads of 128, every third layer windowed
+    (latent of 128 numbers, no positions), the others with a latent of 192 and a rotated part of 64; 32 experts of a
+    quarter of the dense feed-forward each, four of them a token (of the four best of eight groups), so that a token's
+    experts do the work of the dense feed-forward, and a shared expert of the same size beside them."""
+    mlp = {"kind": "moe", "router": {"experts": 32, "top": 4, "groups": {"count": 8, "keep": 4}},
+           "expert": {"ff": ff // 4, "limit": 7.0}, "shared": {"ff": ff // 4, "limit": 7.0}}
+    rotated = {"type": "latent_attention", "mlp": mlp,
+               "mixer": {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "scale": 128 ** -0.5,
+                         "rot": {"base": 1e4, "dims": 64, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+    windowed = {"type": "latent_attention_2", "mlp": mlp,
+                "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 128, "q_rank": max(128, width // 4),
+                          "scale": 128 ** -0.5, "mask": {"size": window}}}
+    pattern = [windowed, rotated, rotated]
+    return {"architecture": "Gonozen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": [pattern[i % 3] for i in range(layers)]}
+
+
+def compare_gonozen(size: str, tokens: int, batch: int, steps: int, warmup: int, hbm_gbs: float, bf16_tflops: float):
+    """The Gonozen design beside the Qwen3 decoder at equal width, layer count and heads, the experts that a token uses
+    as large together as the dense feed-forward: throughput of both, and how far the kernels of the new mechanisms are
+    from their rooflines beside the like kernels of the Qwen3 model.  Rooflines: attention over decoded tokens against
+    the copy bandwidth (every cached vector of the visible keys read once); attention over a prompt against the tensor
+    peak, counting what the kernel computes (scores and weighted means over the cached vector's width for the latents,
+    over the head size for Qwen3; the causal half, or the window's band); the experts' products of a prompt against the
+    tensor peak beside the dense gated product and its down projection; the experts' products of decoded tokens against
+    the copy bandwidth (each pair's expert read once) beside the dense feed-forward's weights read once."""
+    from .config.gonozen_config import GonozenConfig
+    from .config.model_config import Qwen3Config
+    sz = DESIGN_SIZES[size]
+    W, ff, H, G, L, V = sz["width"], sz["ff"], sz["heads"], sz["kv_heads"], sz["layers"], sz["vocab"]
+    raw = gonozen_raw_config(W, ff, H, L, V)
+    new = measure_design(GonozenConfig(raw), tokens, batch, steps, warmup)
+    old = measure_design(Qwen3Config.from_dict(dict(vocab_size=V, hidden_size=W, intermediate_size=ff, num_hidden_layers=L,
+                                                    num_attention_heads=H, num_key_value_heads=G, head_dim=128,
+                                                    rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                                                    max_position_embeddings=32768)), tokens, batch, steps, warmup)
+    frac = lambda work, ms, peak: round(work / (ms * 1e-3) / peak, 4) if ms > 0 else None
+    lat_bytes = lat_flops = 0.0
+    for layer in raw["layers"]:
+        m = layer["mixer"]
+        width = (m["kv_rank"] + m.get("rot_dim", 0) + 15) // 16 * 16
+        window = m.get("mask", {}).get("size")
+        seen = min(tokens, window) if window else tokens
+        lat_bytes += 2.0 * width * seen * batch
+        keys = tokens * tokens / 2 if not window or window >= tokens else tokens * window - window * window / 2
+        lat_flops += 4.0 * keys * H * width
+    mlp = raw["layers"][0]["mlp"]
+    F, top = mlp["expert"]["ff"], mlp["router"]["top"]
+    moe_flops = L * 2.0 * tokens * top * 3 * F * W
+    moe_bytes = L * 2.0 * batch * top * 3 * F * W
+    dense_flops, dense_bytes = L * 2.0 * tokens * 3 * ff * W, L * 2.0 * 3 * ff * W
+    D = 128
+    k_new, k_old = new["prefill_kernels"], old["prefill_kernels"]
+    d_new, d_old = new["decode_kernels"], old["decode_kernels"]
+    att = ("attn_prefill", "merge_key_splits")
+    dec = ("attn_decode", "attn_combine")
+    ff_old_pf = sum(ms for name, ms in k_old.items() if ms >= sorted(k_old.values())[-3] and not any(n in name for n in att))
+    kernels = {
+        "decode_attention_latents": {"ms": round(_kernel_ms(d_new, *dec), 4), "of_hbm": frac(lat_bytes, _kernel_ms(d_new, *dec), hbm_gbs * 1e9)},
+        "decode_attention_qwen3": {"ms": round(_kernel_ms(d_old, *dec), 4),
+                                   "of_hbm": frac(2.0 * 2 * G * D * tokens * batch * L, _kernel_ms(d_old, *dec), hbm_gbs * 1e9)},
+        "prefill_attention_latents": {"ms": round(_kernel_ms(k_new, *att), 4), "of_bf16_peak": frac(lat_flops, _kernel_ms(k_new, *att), bf16_tflops * 1e12)},
+        "prefill_attention_qwen3": {"ms": round(_kernel_ms(k_old, *att), 4),
+                                    "of_bf16_peak": frac(4.0 * tokens * tokens / 2 * H * D * L, _kernel_ms(k_old, *att), bf16_tflops * 1e12)},
+        "prefill_experts": {"ms": round(_kernel_ms(k_new, "moe_grouped_gemm"), 4),
+                            "of_bf16_peak": frac(moe_flops, _kernel_ms(k_new, "moe_grouped_gemm"), bf16_tflops * 1e12)},
+        "prefill_dense_feed_forward_qwen3": {"ms": round(ff_old_pf, 4), "of_bf16_peak": frac(dense_flops, ff_old_pf, bf16_tflops * 1e12),
+                                             "note": "the three largest kernels of the step beside the attention: the gated product and the down projection among them"},
+        "decode_experts": {"ms": round(_kernel_ms(d_new, "moe_pair_linear", "moe_grouped_gemm"), 4),
+                           "of_hbm": frac(moe_bytes, _kernel_ms(d_new, "moe_pair_linear", "moe_grouped_gemm"), hbm_gbs * 1e9)},
+        "decode_weight_streaming_qwen3": {"ms": round(_kernel_ms(d_old, "gemm_skinny"), 4),
+                                          "of_hbm": frac(dense_bytes + L * 2.0 * W * (H + 2 * G + H) * D, _kernel_ms(d_old, "gemm_skinny"), hbm_gbs * 1e9)},
+    }
+    for r in (new, old):
+        del r["prefill_kernels"], r["decode_kernels"]
+    return {"size": size, "width": W, "ff": ff, "heads": H, "layers": L, "tokens": tokens, "batch": batch,
+            "experts": mlp["router"], "expert_ff": F, "gonozen": new, "qwen3": old, "kernels": kernels}

@@ -374,3 +374,25 @@ RB_EXPORT int rb_moe_grouped_gemm(const void* A, int lda, const int* pair_at, in
     return rb_launch_pdl(moe_grouped_gemm_kernel, grid, dim3(256), 0, st, (const bf16*)A, lda, pair_at, in_div, (const bf16*)W,
                          offsets, E, (bf16*)C, ldc, N, K);
 }
+
+// ---------------------------------------------------------------- the tokens' rows in the order of the places
+// out[place, :] = x[pair_at[place] / in_div, :], 16 bytes a thread and step: what a product that wants its rows
+// contiguous (operands by TMA) reads.  Rows of `bytes` bytes, a multiple of 16.
+__global__ void moe_gather_rows_kernel(const unsigned char* __restrict__ x, long long ldx_bytes, const int* __restrict__ pair_at,
+                                       int in_div, unsigned char* __restrict__ out, int bytes) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int place = blockIdx.x;
+    const unsigned char* src = x + (size_t)(pair_at[place] / in_div) * ldx_bytes;
+    unsigned char* dst = out + (size_t)place * bytes;
+    for (int b = threadIdx.x * 16; b < bytes; b += blockDim.x * 16)
+        *reinterpret_cast<uint4*>(dst + b) = *reinterpret_cast<const uint4*>(src + b);
+}
+
+RB_EXPORT int rb_moe_gather_rows(const void* x, long long ldx_bytes, const int* pair_at, int in_div, void* out, int bytes,
+                                 int places, cudaStream_t st) {
+    if (places <= 0) return 0;
+    if (bytes % 16 || ldx_bytes % 16 || ((uintptr_t)x % 16) || ((uintptr_t)out % 16)) return (int)cudaErrorInvalidValue;
+    return rb_launch_pdl(moe_gather_rows_kernel, dim3(places), dim3(128), 0, st, (const unsigned char*)x, ldx_bytes, pair_at,
+                         in_div, (unsigned char*)out, bytes);
+}

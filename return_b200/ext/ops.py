@@ -116,6 +116,7 @@ def build_all():
     paths.append(build.library_path("return_recurrent", _RECURRENT_SOURCES, {"RB_PDL_MODE": PDL_MODE}))
     paths.append(build.library_path("return_latent", _LATENT_SOURCES, {"RB_PDL_MODE": PDL_MODE}))
     paths.append(build.library_path("return_moe", _MOE_SOURCES, {"RB_PDL_MODE": PDL_MODE}))
+    paths.append(build.library_path("return_moe_tc5", _MOE_TC5_SOURCES, {"RB_PDL_MODE": PDL_MODE}))
     for d in TC5_ATTENTION_HEAD_DIMS:
         paths.append(build.library_path(f"return_attn_tc5_d{d}", ["attention_tc5.cu"], _attn_tc5_defines(d)))
     for d in PREBUILT_HEAD_DIMS:
@@ -1111,8 +1112,9 @@ def moe_lib() -> ctypes.CDLL:
         lib.rb_moe_combine.argtypes = [P, P, P, P, P, I, I, I, I, P]
         lib.rb_moe_sort.argtypes = [P, I, I, P, P, P, P]
         lib.rb_moe_grouped_gemm.argtypes = [P, I, P, I, P, P, I, P, I, I, I, I, P]
+        lib.rb_moe_gather_rows.argtypes = [P, ctypes.c_longlong, P, I, P, I, I, P]
         for name in ("rb_moe_route", "rb_moe_pair_linear", "rb_clamped_glu", "rb_moe_combine", "rb_moe_sort",
-                     "rb_moe_grouped_gemm"):
+                     "rb_moe_grouped_gemm", "rb_moe_gather_rows"):
             getattr(lib, name).restype = c_int
         _moe = lib
     return _moe
@@ -1181,9 +1183,48 @@ def moe_grouped_gemm(x, pair_at, in_div: int, w, offsets, out) -> None:
                                          out.stride(0), places, N, K, _stream()), "moe_grouped_gemm")
 
 
+_moe_tc5 = None
+_MOE_TC5_SOURCES = ["moe_tc5.cu"]
+
+
+def moe_tc5_lib() -> ctypes.CDLL:
+    """The experts' products of a prompt on tcgen05 (csrc/moe_tc5.cu); compiled when a prompt first needs it."""
+    global _moe_tc5
+    if _moe_tc5 is None:
+        lib = build.load("return_moe_tc5", _MOE_TC5_SOURCES, {"RB_PDL_MODE": PDL_MODE})
+        P, I = c_void_p, c_int
+        lib.rb_moe_tc5_gemm.argtypes = [P, I, P, P, I, P, I, I, I, I, P, P]
+        lib.rb_moe_tc5_gemm.restype = c_int
+        _moe_tc5 = lib
+    return _moe_tc5
+
+
+def moe_gather_rows(x, pair_at, in_div: int, out) -> None:
+    """out[place] = x[pair_at[place] // in_div]: the tokens' rows in the order of the places."""
+    places, K = out.shape
+    assert x.dtype == out.dtype and x.stride(1) == 1 and out.is_contiguous() and x.shape[1] == K and pair_at.numel() == places
+    size = x.element_size()
+    _check(moe_lib().rb_moe_gather_rows(_ptr(x), x.stride(0) * size, _ptr(pair_at), in_div, _ptr(out), K * size, places,
+                                        _stream()), "moe_gather_rows")
+
+
+def moe_tc5_gemm(x_sorted, w, offsets, out) -> None:
+    """out[place] = x_sorted[place] @ w[expert of the place]^T on tcgen05 (TMA-fed), bfloat16; w [E, N, K]."""
+    E, N, K = w.shape
+    places = out.shape[0]
+    assert x_sorted.dtype == w.dtype == out.dtype == torch.bfloat16 and x_sorted.stride(1) == 1 and w.is_contiguous()
+    assert x_sorted.shape == (places, K) and out.shape[1] == N and out.stride(1) == 1
+    _tc5_launched.add(x_sorted.device)
+    _check(moe_tc5_lib().rb_moe_tc5_gemm(_ptr(x_sorted), x_sorted.stride(0), _ptr(w), _ptr(offsets), E, _ptr(out), out.stride(0),
+                                         places, N, K, _ptr(tc5_status(x_sorted.device)), _stream()), "moe_tc5_gemm")
+
+
 # From this many (token, expert) pairs on, a step's experts run as tiles on the tensor cores over the pairs sorted by
 # expert; below, every pair streams its expert's weights (a step of decoded tokens: few pairs, most on experts of their own).
 MOE_GROUPED_MIN_PAIRS = 64
+# From this many pairs on the tiles are those of the tcgen05 kernel (128 places x 256 columns, operands by TMA, the
+# tokens' rows gathered into the order of the places first); between the two, mma.sync tiles of 64 x 128.
+MOE_TC5_MIN_PAIRS = 1024
 
 
 def moe_experts(x, gate_up, down, expert_of, weight, shared, out, limit: float, alpha: float, ctx=None) -> None:
@@ -1206,9 +1247,16 @@ def moe_experts(x, gate_up, down, expert_of, weight, shared, out, limit: float, 
         pair_at = buf("moe.pair_at", (pairs,), torch.int32)
         place_of = buf("moe.place_of", (pairs,), torch.int32)
         moe_sort(expert_of, E, offsets, pair_at, place_of)
-        moe_grouped_gemm(x, pair_at, top, gate_up, offsets, gu)
-        clamped_glu(gu, act, limit, alpha)
-        moe_grouped_gemm(act, None, 1, down, offsets, y)
+        if pairs >= MOE_TC5_MIN_PAIRS and E <= 1024:
+            rows = buf("moe.pair_rows", (pairs, H))
+            moe_gather_rows(x, pair_at, top, rows)
+            moe_tc5_gemm(rows, gate_up, offsets, gu)
+            clamped_glu(gu, act, limit, alpha)
+            moe_tc5_gemm(act, down, offsets, y)
+        else:
+            moe_grouped_gemm(x, pair_at, top, gate_up, offsets, gu)
+            clamped_glu(gu, act, limit, alpha)
+            moe_grouped_gemm(act, None, 1, down, offsets, y)
         moe_combine(y, weight, shared, out, row_of=place_of)
         return
     moe_pair_linear(x, top, gate_up, expert_of, gu)

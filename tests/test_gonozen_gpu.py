@@ -203,6 +203,71 @@ def test_output_norm_add_input_norm(dtype):
     assert torch.equal(s2, s)
 
 
+@pytest.mark.parametrize("N,K,counts", [(200, 72, (130, 0, 1, 64, 105)), (128, 32, (64,)), (24, 8, (3, 70, 0, 0, 129, 1))])
+def test_experts_products_as_sorted_tiles(N, K, counts):
+    """The experts' products over the pairs sorted by expert, on the tensor cores, against float64: experts without a
+    pair, runs that end inside a tile, output widths and depths that fill no whole tile; rows gathered through the order."""
+    from return_b200.ext import ops
+    g = torch.Generator().manual_seed(N)
+    E, top = len(counts), 2
+    expert_of = torch.cat([torch.full((c,), e, dtype=torch.int32) for e, c in enumerate(counts)])
+    expert_of = expert_of[torch.randperm(expert_of.numel(), generator=g)]
+    if expert_of.numel() % top:
+        expert_of = torch.cat([expert_of, expert_of[:1]])
+    pairs = expert_of.numel()
+    x = torch.randn((pairs // top, K), generator=g).bfloat16()
+    w = (torch.randn((E, N, K), generator=g) * K ** -0.5).bfloat16()
+    offsets = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    pair_at, place_of = torch.empty(pairs, dtype=torch.int32, device="cuda"), torch.empty(pairs, dtype=torch.int32, device="cuda")
+    ops.moe_sort(expert_of.cuda(), E, offsets, pair_at, place_of)
+    assert offsets.cpu().tolist() == [0] + torch.bincount(expert_of.long(), minlength=E).cumsum(0).tolist()
+    assert torch.equal(pair_at[place_of.long()].cpu(), torch.arange(pairs, dtype=torch.int32))
+    assert torch.equal(expert_of[pair_at.cpu().long()], expert_of.sort().values)
+    out = torch.full((pairs, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.moe_grouped_gemm(x.cuda(), pair_at, top, w.cuda(), offsets, out)
+    rows = pair_at.cpu().long()
+    want = torch.einsum("pk,pnk->pn", x.double()[rows // top], w.double()[expert_of.long()[rows]])
+    assert torch.allclose(out.cpu().double(), want, rtol=2e-2, atol=2e-2)
+    # the second product reads rows where they lie; and the weighted sum finds a pair's row through the order
+    out2 = torch.full((pairs, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    xs = torch.randn((pairs, K), generator=g).bfloat16()
+    ops.moe_grouped_gemm(xs.cuda(), None, 1, w.cuda(), offsets, out2)
+    want2 = torch.einsum("pk,pnk->pn", xs.double(), w.double()[expert_of.long()[rows]])
+    assert torch.allclose(out2.cpu().double(), want2, rtol=2e-2, atol=2e-2)
+    weight = torch.rand((pairs // top, top), generator=g)
+    y = torch.empty((pairs // top, N), dtype=torch.bfloat16, device="cuda")
+    ops.moe_combine(out2, weight.cuda(), None, y, row_of=place_of)
+    want_y = (weight.double()[:, :, None] * out2.cpu().double()[place_of.cpu().long()].view(pairs // top, top, N)).sum(1)
+    assert torch.allclose(y.cpu().double(), want_y, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("N,K,counts", [(200, 72, (130, 0, 1, 64, 300)), (512, 128, (128, 256)), (24, 8, (3, 70, 0, 0, 129, 1)),
+                                        (300, 320, (1,) * 40 + (0,) * 3 + (500,))])
+def test_experts_products_on_tcgen05(N, K, counts):
+    """The tcgen05 form of the experts' products (rows in the order of the places, operands by TMA) against float64:
+    runs that end inside a tile of 128, experts without a pair, many experts of one pair, output widths and depths
+    that fill no whole tile or k block, a tile whose box of weight rows reaches past the last expert."""
+    from return_b200.ext import ops
+    g = torch.Generator().manual_seed(N + K)
+    E = len(counts)
+    expert_sorted = torch.cat([torch.full((c,), e, dtype=torch.int64) for e, c in enumerate(counts)])
+    places = expert_sorted.numel()
+    offsets = torch.tensor([0] + torch.bincount(expert_sorted, minlength=E).cumsum(0).tolist(), dtype=torch.int32)
+    x = torch.randn((places, K), generator=g).bfloat16()
+    w = (torch.randn((E, N, K), generator=g) * K ** -0.5).bfloat16()
+    out = torch.full((places, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.moe_tc5_gemm(x.cuda(), w.cuda(), offsets.cuda(), out)
+    ops.check_status("cuda:0")
+    want = torch.einsum("pk,pnk->pn", x.double(), w.double()[expert_sorted])
+    assert torch.allclose(out.cpu().double(), want, rtol=2e-2, atol=2e-2)
+    # the gather that feeds it
+    pair_at = torch.randperm(places * 1, generator=g).int()
+    src = torch.randn((places // 2 + 1, K), generator=g).bfloat16()
+    rows = torch.empty((places, K), dtype=torch.bfloat16, device="cuda")
+    ops.moe_gather_rows(src.cuda(), pair_at.cuda(), 2, rows)
+    assert torch.equal(rows.cpu(), src[pair_at.long() // 2])
+
+
 def test_soft_cap():
     from return_b200.ext import ops
     x = torch.linspace(-60, 60, 1001)
