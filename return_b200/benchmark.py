@@ -601,7 +601,8 @@ def compare_gonozen(size: str, tokens: int, batch: int, steps: int, warmup: int,
                                                     rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
                                                     max_position_embeddings=32768)), tokens, batch, steps, warmup)
     frac = lambda work, ms, peak: round(work / (ms * 1e-3) / peak, 4) if ms > 0 else None
-    lat_bytes = lat_flops = 0.0
+    lat_bytes = 0.0
+    lat_flops = {"tcgen05": 0.0, "mma_sync": 0.0}          # by the kernel that a cached vector's width runs on
     for layer in raw["layers"]:
         m = layer["mixer"]
         width = (m["kv_rank"] + m.get("rot_dim", 0) + 15) // 16 * 16
@@ -609,27 +610,33 @@ def compare_gonozen(size: str, tokens: int, batch: int, steps: int, warmup: int,
         seen = min(tokens, window) if window else tokens
         lat_bytes += 2.0 * width * seen * batch
         keys = tokens * tokens / 2 if not window or window >= tokens else tokens * window - window * window / 2
-        lat_flops += 4.0 * keys * H * width
+        lat_flops["tcgen05" if width in (64, 128) else "mma_sync"] += 4.0 * keys * H * width
     mlp = raw["layers"][0]["mlp"]
     F, top = mlp["expert"]["ff"], mlp["router"]["top"]
     moe_flops = L * 2.0 * tokens * top * 3 * F * W
-    moe_bytes = L * 2.0 * batch * top * 3 * F * W
+    E = mlp["router"]["experts"]
+    distinct = E * (1.0 - (1.0 - 1.0 / E) ** (batch * top))     # experts that a step's pairs reach, if they chose evenly
+    moe_bytes = L * 2.0 * distinct * 3 * F * W
     dense_flops, dense_bytes = L * 2.0 * tokens * 3 * ff * W, L * 2.0 * 3 * ff * W
     D = 128
     k_new, k_old = new["prefill_kernels"], old["prefill_kernels"]
     d_new, d_old = new["decode_kernels"], old["decode_kernels"]
     att = ("attn_prefill", "merge_key_splits")
+    att_tc5, att_mma = ("attn_prefill_tc5", "merge_key_splits"), ("attn_prefill_kernel",)
     dec = ("attn_decode", "attn_combine")
     ff_old_pf = sum(ms for name, ms in k_old.items() if ms >= sorted(k_old.values())[-3] and not any(n in name for n in att))
     kernels = {
         "decode_attention_latents": {"ms": round(_kernel_ms(d_new, *dec), 4), "of_hbm": frac(lat_bytes, _kernel_ms(d_new, *dec), hbm_gbs * 1e9)},
         "decode_attention_qwen3": {"ms": round(_kernel_ms(d_old, *dec), 4),
                                    "of_hbm": frac(2.0 * 2 * G * D * tokens * batch * L, _kernel_ms(d_old, *dec), hbm_gbs * 1e9)},
-        "prefill_attention_latents": {"ms": round(_kernel_ms(k_new, *att), 4), "of_bf16_peak": frac(lat_flops, _kernel_ms(k_new, *att), bf16_tflops * 1e12)},
+        "prefill_attention_latents_of_128_tcgen05": {"ms": round(_kernel_ms(k_new, *att_tc5), 4),
+                                                     "of_bf16_peak": frac(lat_flops["tcgen05"], _kernel_ms(k_new, *att_tc5), bf16_tflops * 1e12)},
+        "prefill_attention_latents_of_256_mma_sync": {"ms": round(_kernel_ms(k_new, *att_mma), 4),
+                                                      "of_bf16_peak": frac(lat_flops["mma_sync"], _kernel_ms(k_new, *att_mma), bf16_tflops * 1e12)},
         "prefill_attention_qwen3": {"ms": round(_kernel_ms(k_old, *att), 4),
                                     "of_bf16_peak": frac(4.0 * tokens * tokens / 2 * H * D * L, _kernel_ms(k_old, *att), bf16_tflops * 1e12)},
-        "prefill_experts": {"ms": round(_kernel_ms(k_new, "moe_grouped_gemm"), 4),
-                            "of_bf16_peak": frac(moe_flops, _kernel_ms(k_new, "moe_grouped_gemm"), bf16_tflops * 1e12)},
+        "prefill_experts": {"ms": round(_kernel_ms(k_new, "moe_grouped_gemm", "moe_tc5"), 4),
+                            "of_bf16_peak": frac(moe_flops, _kernel_ms(k_new, "moe_grouped_gemm", "moe_tc5"), bf16_tflops * 1e12)},
         "prefill_dense_feed_forward_qwen3": {"ms": round(ff_old_pf, 4), "of_bf16_peak": frac(dense_flops, ff_old_pf, bf16_tflops * 1e12),
                                              "note": "the three largest kernels of the step beside the attention: the gated product and the down projection among them"},
         "decode_experts": {"ms": round(_kernel_ms(d_new, "moe_pair_linear", "moe_grouped_gemm"), 4),

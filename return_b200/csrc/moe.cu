@@ -125,6 +125,63 @@ moe_pair_linear_kernel(const TA* __restrict__ x, int ldx, int in_div, const TA* 
     }
 }
 
+// The bfloat16 form for rows of whole 16-byte pieces: a lane reads eight weights at a time from each of four output
+// rows (four loads in flight, 512 bytes a row and step over the warp), the token's row waits in shared memory as
+// float32.  Eight warps share 64 output rows; the sums keep one order (a lane's pieces in turn, then the butterfly).
+__global__ void __launch_bounds__(256)
+moe_pair_linear_vec_kernel(const bf16* __restrict__ x, int ldx, int in_div, const bf16* __restrict__ W,
+                           const int* __restrict__ expert_of, bf16* __restrict__ out, int ldo, int N, int K) {
+    extern __shared__ __align__(16) float xs[];           // K floats
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bf16* xr = x + (size_t)(i / in_div) * ldx;
+    for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr + k);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(p[j]);
+            xs[k + 2 * j] = f.x;
+            xs[k + 2 * j + 1] = f.y;
+        }
+    }
+    __syncthreads();
+    const bf16* We = W + (size_t)expert_of[i] * N * K;
+    const int n_base = blockIdx.y * 64 + warp * 8;
+#pragma unroll 1
+    for (int r0 = 0; r0 < 8; r0 += 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const bf16* wr[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wr[j] = We + (size_t)min(n_base + r0 + j, N - 1) * K;      // a row past the end reads the last one
+        for (int k = lane * 8; k < K; k += 256) {
+            uint4 wv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const uint4*>(wr[j] + k);
+            const float4 xa = *reinterpret_cast<const float4*>(xs + k), xb = *reinterpret_cast<const float4*>(xs + k + 4);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&wv[j]);
+                const float2 w0 = __bfloat1622float2(p[0]), w1 = __bfloat1622float2(p[1]);
+                const float2 w2 = __bfloat1622float2(p[2]), w3 = __bfloat1622float2(p[3]);
+                acc[j] = fmaf(xa.x, w0.x, acc[j]); acc[j] = fmaf(xa.y, w0.y, acc[j]);
+                acc[j] = fmaf(xa.z, w1.x, acc[j]); acc[j] = fmaf(xa.w, w1.y, acc[j]);
+                acc[j] = fmaf(xb.x, w2.x, acc[j]); acc[j] = fmaf(xb.y, w2.y, acc[j]);
+                acc[j] = fmaf(xb.z, w3.x, acc[j]); acc[j] = fmaf(xb.w, w3.y, acc[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float v = warp_sum(acc[j]);
+            const int n = n_base + r0 + j;
+            if (lane == 0 && n < N) out[(size_t)i * ldo + n] = __float2bfloat16_rn(v);
+        }
+    }
+    pdl_trigger_late();
+}
+
 RB_EXPORT int rb_moe_pair_linear(const void* x, int ldx, int in_div, const void* W, const int* expert_of, void* out, int ldo,
                                  int act_dtype, int pairs, int N, int K, cudaStream_t st) {
     if (pairs <= 0 || N <= 0) return 0;
@@ -132,6 +189,9 @@ RB_EXPORT int rb_moe_pair_linear(const void* x, int ldx, int in_div, const void*
     dim3 grid(pairs, (N + rows_per_cta - 1) / rows_per_cta);
     const size_t smem = (size_t)K * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if (act_dtype == RB_BF16 && K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)W % 16) == 0)
+        return rb_launch_pdl(moe_pair_linear_vec_kernel, grid, dim3(256), smem, st, (const bf16*)x, ldx, in_div, (const bf16*)W,
+                             expert_of, (bf16*)out, ldo, N, K);
     if (act_dtype == RB_F32)
         return rb_launch_pdl(moe_pair_linear_kernel<float, float>, grid, dim3(256), smem, st, (const float*)x, ldx, in_div,
                              (const float*)W, expert_of, (float*)out, ldo, N, K, rows_per_cta);
@@ -156,10 +216,40 @@ __global__ void clamped_glu_kernel(const TA* __restrict__ in, int ldi, TA* __res
     }
 }
 
+// bfloat16 with F a multiple of 8: eight outputs (two 16-byte loads, one store) a thread and step.
+__global__ void clamped_glu_bf16x8_kernel(const bf16* __restrict__ in, int ldi, bf16* __restrict__ out, int ldo, int F8,
+                                          float limit, float alpha, unsigned total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        const unsigned r = e / F8, f = (e - r * F8) * 8;
+        const uint4 gv = *reinterpret_cast<const uint4*>(in + (size_t)r * ldi + f);
+        const uint4 uv = *reinterpret_cast<const uint4*>(in + (size_t)r * ldi + F8 * 8 + f);
+        const bf16* g8 = reinterpret_cast<const bf16*>(&gv);
+        const bf16* u8 = reinterpret_cast<const bf16*>(&uv);
+        uint4 ov;
+        bf16* o8 = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float g = fminf(__bfloat162float(g8[k]), limit);
+            const float u = fminf(fmaxf(__bfloat162float(u8[k]), -limit), limit);
+            o8[k] = __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)r * ldo + f) = ov;
+    }
+}
+
 RB_EXPORT int rb_clamped_glu(const void* in, int ldi, void* out, int ldo, int act_dtype, int rows, int F, float limit,
                              float alpha, cudaStream_t st) {
     const long long total = (long long)rows * F;
     if (total <= 0) return 0;
+    if (act_dtype == RB_BF16 && F % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)in % 16) == 0 &&
+        ((uintptr_t)out % 16) == 0 && total / 8 < 0x7fffffffLL) {
+        const unsigned items = (unsigned)(total / 8);
+        const int nblocks = (int)min((unsigned)(148 * 16), (items + 255) / 256);
+        return rb_launch_pdl(clamped_glu_bf16x8_kernel, dim3(nblocks), dim3(256), 0, st, (const bf16*)in, ldi, (bf16*)out, ldo,
+                             F / 8, limit, alpha, items);
+    }
     const int blocks = (int)min((long long)4096, (total + 255) / 256);
     if (act_dtype == RB_F32)
         return rb_launch_pdl(clamped_glu_kernel<float>, dim3(blocks), dim3(256), 0, st, (const float*)in, ldi, (float*)out, ldo, F,
