@@ -281,6 +281,37 @@ def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0, impl=0) -> D
             "TFLOPs": 2.0 * M * N * K / ms / 1e9}
 
 
+def kernel_experts(tokens=2048, top=4, experts=32, N=3072, K=2048, iters=10, warmup=3, impl=0, pairs=0) -> Dict[str, object]:
+    """The experts' product alone over (token, expert) pairs sorted by expert, the tokens choosing evenly at random:
+    ``impl`` 0: the tcgen05 kernel; 1: the mma.sync tiles; 2: a pair streams its expert's rows (decoded tokens; give
+    ``pairs``).  Device time, TFLOP/s, and the bandwidth of the experts' weights that the pairs reach."""
+    from .ext import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(3)
+    n_pairs = pairs or tokens * top
+    expert_of = torch.randint(0, experts, (n_pairs,), generator=g).int()
+    offsets = torch.tensor([0] + torch.bincount(expert_of.long(), minlength=experts).cumsum(0).tolist(), dtype=torch.int32).to(dev)
+    order = expert_of.sort(stable=True).indices.int().to(dev)
+    expert_dev = expert_of.to(dev)
+    reached = int(expert_of.unique().numel())
+    fns = []
+    for _ in range(_copies_beyond_l2(experts * N * K * 2)):
+        x = torch.randn((n_pairs, K), device=dev).bfloat16()
+        w = (torch.randn((experts, N, K), device=dev) * K ** -0.5).bfloat16()
+        out = torch.empty((n_pairs, N), dtype=torch.bfloat16, device=dev)
+        if impl == 0:
+            fns.append(lambda a=(x, w, out): ops.moe_tc5_gemm(a[0], a[1], offsets, a[2]))
+        elif impl == 1:
+            fns.append(lambda a=(x, w, out): ops.moe_grouped_gemm(a[0], order, 1, a[1], offsets, a[2]))
+        else:
+            fns.append(lambda a=(x, w, out): ops.moe_pair_linear(a[0], 1, a[1], expert_dev, a[2]))
+    ms = _time_kernels(fns, iters, warmup)
+    ops.check_status(dev)
+    return {"kernel": ("moe_tc5", "moe_grouped_mma", "moe_pair_linear")[impl], "pairs": n_pairs, "experts": experts,
+            "experts_reached": reached, "N": N, "K": K, "ms": ms, "TFLOPs": 2.0 * n_pairs * N * K / ms / 1e9,
+            "GBps_of_reached_weights": reached * N * K * 2 / ms / 1e6}
+
+
 def kernel_elementwise(rows=2048, hidden=4096, intermediate=12288, iters=10, warmup=3) -> Dict[str, object]:
     """The residual add + RMSNorm kernel and the SwiGLU kernel alone, over buffers larger than L2: device time and
     the bandwidth of what each must read and write (norm: stream in and out in float32, delta in, normed rows out;

@@ -112,7 +112,7 @@ def cmd_kernel_bench(args) -> int:
     from . import benchmark
     fn = {"attention_decode": benchmark.kernel_attention_decode, "attention_prefill": benchmark.kernel_attention_prefill,
           "gemm": benchmark.kernel_gemm, "gated": benchmark.kernel_gated, "elementwise": benchmark.kernel_elementwise,
-          "scan": benchmark.kernel_scan}[args.kernel]
+          "scan": benchmark.kernel_scan, "experts": benchmark.kernel_experts}[args.kernel]
     kw = {}
     for item in args.set or []:
         k, v = item.split("=")
@@ -181,7 +181,7 @@ def main(argv=None) -> int:
     wl.set_defaults(fn=cmd_workload)
 
     k = sub.add_parser("kernel-bench", help="time one kernel alone on random data (for profiles)")
-    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm", "gated", "elementwise", "scan"])
+    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm", "gated", "elementwise", "scan", "experts"])
     k.add_argument("--set", action="append", help="an integer argument of the kernel case, e.g. batch=64 ctx=2048 M=8")
     k.set_defaults(fn=cmd_kernel_bench)
 
