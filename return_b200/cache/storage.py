@@ -6,7 +6,9 @@ hence a page pool, a free list and block tables (``return_b200/cache/manager.py`
 a group is one tensor ``[layers, 2, num_pages, Hkv, page_size, D]`` in the activation dtype
 (index 0 of the second axis: keys, 1: values), so one page id addresses a slab in every layer of
 the group, as in the reference (rollout/cache.py:19-24), and one (page, kv head) tile is
-contiguous.  A mixer that asks for state of fixed size gets ``[max_reside + 1, *shape]``, one row per
+contiguous.  A mixer whose cache is one vector a token (``LatentCacheNeed``: a latent that is key and value for all
+heads) gets a group of its own kind by (window, width) and one tensor ``[layers, num_pages, page_size, width]``.
+A mixer that asks for state of fixed size gets ``[max_reside + 1, *shape]``, one row per
 request slot and a last one that belongs to no request (the padding rows of a captured decode step
 point at it) (after rollout/cache.py:340-360).
 """

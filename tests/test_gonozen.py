@@ -100,17 +100,18 @@ def test_a_random_checkpoint_fills_every_parameter(tmp_path):
 
 
 def test_ramped_rotary_tables_follow_the_plain_frequencies():
-    rot = {"base": 20000.0, "dims": 32, "scaling": {"factor": 2.0, "original": 512, "fast": 32.0, "slow": 1.0}}
-    spec = RampedRopeSpec(rotary_dim=32, theta=20000.0, max_positions=300, factor=2.0, original=512, fast=32.0, slow=1.0)
+    rot = {"base": 5000.0, "dims": 24, "scaling": {"factor": 3.0, "original": 256, "fast": 16.0, "slow": 2.0}}
+    spec = RampedRopeSpec(rotary_dim=24, theta=5000.0, max_positions=300, factor=3.0, original=256, fast=16.0, slow=2.0)
     cos, sin, width = RampedRotaryEncoding(spec, BuildEnv(torch.float32, torch.device("cpu"))).rotary_tables()
     f, mag = plain.rotary_frequencies(rot)
-    assert width == 32 and mag == pytest.approx(0.1 * math.log(2.0) + 1.0)
+    assert width == 24 and mag == pytest.approx(0.1 * math.log(3.0) + 1.0)
     ang = torch.outer(torch.arange(300, dtype=torch.float64), f)
     assert torch.allclose(cos.double(), ang.cos() * mag, atol=1e-6) and torch.allclose(sin.double(), ang.sin() * mag, atol=1e-6)
     # the fast pairs keep their frequency, the slow ones are divided by the factor, and between them lies a ramp
-    plain_f = 20000.0 ** (-2.0 * torch.arange(16, dtype=torch.float64) / 32)
+    plain_f = 5000.0 ** (-2.0 * torch.arange(12, dtype=torch.float64) / 24)
     ratio = f / plain_f
-    assert ratio[0] == 1.0 and ratio[-1] == pytest.approx(0.5) and (ratio[1:] <= ratio[:-1] + 1e-12).all()
+    assert ratio[0] == 1.0 and ratio[-1] == pytest.approx(1.0 / 3.0) and (ratio[1:] <= ratio[:-1] + 1e-12).all()
+    assert ((ratio > 1.0 / 3.0 + 1e-9) & (ratio < 1.0 - 1e-9)).any()          # some pair lies on the ramp
     # without stretching: plain frequencies and no factor
     spec = RampedRopeSpec(rotary_dim=8, theta=100.0, max_positions=10)
     cos, sin, _ = RampedRotaryEncoding(spec, BuildEnv(torch.float32, torch.device("cpu"))).rotary_tables()
@@ -119,15 +120,15 @@ def test_ramped_rotary_tables_follow_the_plain_frequencies():
 
 def test_latents_get_page_groups_of_their_own_by_width_and_window():
     env = BuildEnv(torch.float32, torch.device("cpu"))
-    needs = [LatentCacheNeed(96, 72), LatentCacheNeed(160, None), LatentCacheNeed(160, None), LatentCacheNeed(96, 72),
-             KVCacheNeed(2, 160, None), None]
+    needs = [LatentCacheNeed(80, 50), LatentCacheNeed(144, None), LatentCacheNeed(144, None), LatentCacheNeed(80, 50),
+             KVCacheNeed(2, 144, None), None]
     st = CacheStorage(needs, page_size=16, num_pages=40, max_reside=4, env=env, longest_append=64)
-    assert [g.name for g in st.group_specs] == ["window72_latent96", "full_latent160", "full_h2_d160"]
-    assert st.group_specs[0].num_pages == 4 * ((72 + 64 + 15) // 16 + 1) and st.group_specs[1].num_pages == 40
+    assert [g.name for g in st.group_specs] == ["window50_latent80", "full_latent144", "full_h2_d144"]
+    assert st.group_specs[0].num_pages == 4 * ((50 + 64 + 15) // 16 + 1) and st.group_specs[1].num_pages == 40
     st.allocate()
-    assert tuple(st.pools[0].shape) == (2, st.group_specs[0].num_pages, 16, 96)        # one tensor: a latent is key and value
-    assert tuple(st.pools[1].shape) == (2, 40, 16, 160) and tuple(st.pools[2].shape) == (1, 2, 40, 2, 16, 160)
-    assert st.bytes_per_token() == (2 * 96 + 2 * 160 + 2 * 2 * 160) * 4
+    assert tuple(st.pools[0].shape) == (2, st.group_specs[0].num_pages, 16, 80)        # one tensor: a latent is key and value
+    assert tuple(st.pools[1].shape) == (2, 40, 16, 144) and tuple(st.pools[2].shape) == (1, 2, 40, 2, 16, 144)
+    assert st.bytes_per_token() == (2 * 80 + 2 * 144 + 2 * 2 * 144) * 4
     manager = st.make_manager()
     manager.add("a")
     manager.append("a", 200)
@@ -136,10 +137,10 @@ def test_latents_get_page_groups_of_their_own_by_width_and_window():
     class Batch:
         block_tables = [torch.zeros((1, 13), dtype=torch.int32)] * 3
     ctx = st.layer_context(3, Batch(), True)
-    assert ctx.kv.v is None and tuple(ctx.kv.k.shape) == (st.group_specs[0].num_pages, 16, 96)
+    assert ctx.kv.v is None and tuple(ctx.kv.k.shape) == (st.group_specs[0].num_pages, 16, 80)
     assert ctx.kv.k.data_ptr() == st.pools[0][1].data_ptr()
     # the window gave the first pages back while the full group holds them all
-    assert manager.block_table("a", 0)[:9] == [-1] * 8 + [8] and -1 not in manager.block_table("a", 1)
+    assert manager.block_table("a", 0)[:10] == [-1] * 9 + [9] and -1 not in manager.block_table("a", 1)
 
 
 def test_plain_model_is_causal_and_its_window_and_sink_do_what_they_say():
