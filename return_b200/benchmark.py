@@ -641,7 +641,11 @@ def compare_gonozen(size: str, tokens: int, batch: int, steps: int, warmup: int,
         seen = min(tokens, window) if window else tokens
         lat_bytes += 2.0 * width * seen * batch
         keys = tokens * tokens / 2 if not window or window >= tokens else tokens * window - window * window / 2
-        lat_flops["tcgen05" if width in (64, 128) else "mma_sync"] += 4.0 * keys * H * width
+        head = (max(m["dim"] + m.get("rot_dim", 0), m["vdim"]) + 15) // 16 * 16
+        if head in (64, 128) and head < width:             # a prompt runs with keys and values written out per head
+            lat_flops["tcgen05"] += 4.0 * keys * H * head
+        else:
+            lat_flops["tcgen05" if width in (64, 128) else "mma_sync"] += 4.0 * keys * H * width
     mlp = raw["layers"][0]["mlp"]
     F, top = mlp["expert"]["ff"], mlp["router"]["top"]
     moe_flops = L * 2.0 * tokens * top * 3 * F * W
@@ -660,6 +664,8 @@ def compare_gonozen(size: str, tokens: int, batch: int, steps: int, warmup: int,
         "decode_attention_latents": {"ms": round(_kernel_ms(d_new, *dec), 4), "of_hbm": frac(lat_bytes, _kernel_ms(d_new, *dec), hbm_gbs * 1e9)},
         "decode_attention_qwen3": {"ms": round(_kernel_ms(d_old, *dec), 4),
                                    "of_hbm": frac(2.0 * 2 * G * D * tokens * batch * L, _kernel_ms(d_old, *dec), hbm_gbs * 1e9)},
+        "prefill_attention_written_out": {"ms": round(_kernel_ms(k_new, "latent_expand", "latent_gather", "latent_take"), 4),
+                                          "note": "gather, scatter and take-values kernels of the expanded form; its product is a library kernel"},
         "prefill_attention_latents_of_128_tcgen05": {"ms": round(_kernel_ms(k_new, *att_tc5), 4),
                                                      "of_bf16_peak": frac(lat_flops["tcgen05"], _kernel_ms(k_new, *att_tc5), bf16_tflops * 1e12)},
         "prefill_attention_latents_of_256_mma_sync": {"ms": round(_kernel_ms(k_new, *att_mma), 4),

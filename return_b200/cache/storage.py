@@ -135,7 +135,7 @@ class CacheStorage:
                 views = self._layer_views[place] = ((pool[layer], None) if self._group_shape[g][0] == 0 else
                                                     (pool[layer, 0], pool[layer, 1]))
             ctx.kv = KVView(k=views[0], v=views[1], block_table=batch.block_tables[g],
-                            page_size=self.group_specs[g].page_size)
+                            page_size=self.group_specs[g].page_size, group=g)
         if key in self.states:
             ctx.state = self.states[key]
         names = self._composite.get(key)

@@ -290,3 +290,101 @@ RB_EXPORT int rb_gemm_f32_heads(const float* A, const float* W, float* C, int ba
     dim3 grid((N + HB_BN - 1) / HB_BN, (M + HB_BM - 1) / HB_BM, batch);
     return rb_launch_pdl(gemm_f32_heads_kernel, grid, dim3(256), 0, st, A, W, C, M, N, K, lda, ldw, ldc, sa, sw, sc);
 }
+
+// ---------------------------------------------------------------- a prompt's keys and values, expanded per head
+// A long portion of a prompt is cheaper with the heads' keys and values written out (a head then scores dim + rot
+// numbers a key and averages vdim, not twice the cached vector's width): the visible latents are gathered, carried
+// through [U; V] by one product, and scattered here into scratch pools [pages, heads, page_size, head] that the
+// paged tensor-core attention reads with the request's own block table.  Key of head h: [U_h c | rotated part | 0],
+// value: [V_h c | 0].  slot = page * page_size + row, one per gathered latent.
+__global__ void latent_expand_scatter_kernel(const bf16* __restrict__ kv, int ldkv, const bf16* __restrict__ lat, int ldl,
+                                             int rank, int rot, const int* __restrict__ slots, int page_size,
+                                             bf16* __restrict__ kx, bf16* __restrict__ vx, int heads, int dim, int vdim,
+                                             int head) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x;
+    const int slot = slots[i];
+    const int page = slot / page_size, row = slot - page * page_size;
+    const bf16* kvr = kv + (size_t)i * ldkv;
+    const bf16* lr = lat + (size_t)i * ldl + rank;
+    const bf16 zero = __float2bfloat16_rn(0.f);
+    for (int e = threadIdx.x; e < heads * head; e += blockDim.x) {
+        const int h = e / head, d = e - h * head;
+        const size_t at = (((size_t)page * heads + h) * page_size + row) * head + d;
+        kx[at] = d < dim ? kvr[h * dim + d] : (d < dim + rot ? lr[d - dim] : zero);
+        vx[at] = d < vdim ? kvr[heads * dim + h * vdim + d] : zero;
+    }
+}
+
+RB_EXPORT int rb_latent_expand_scatter(const void* kv, int ldkv, const void* lat, int ldl, int rank, int rot, const int* slots,
+                                       int page_size, void* kx, void* vx, int heads, int dim, int vdim, int head, int n,
+                                       cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (head < dim + rot || head < vdim) return (int)cudaErrorInvalidValue;
+    return rb_launch_pdl(latent_expand_scatter_kernel, dim3(n), dim3(256), 0, st, (const bf16*)kv, ldkv, (const bf16*)lat, ldl,
+                         rank, rot, slots, page_size, (bf16*)kx, (bf16*)vx, heads, dim, vdim, head);
+}
+
+// The queries of the expanded form: head h of token t is [its unrotated part | its rotated part, already turned (it
+// lies in the folded query row behind the latent's columns) | 0].
+__global__ void latent_expand_query_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ q_abs, int width,
+                                           int rank, bf16* __restrict__ qx, int heads, int dim, int rot, int head) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const bf16 zero = __float2bfloat16_rn(0.f);
+    for (int e = threadIdx.x; e < heads * head; e += blockDim.x) {
+        const int h = e / head, d = e - h * head;
+        qx[(size_t)t * heads * head + e] = d < dim ? q[(size_t)t * ldq + (size_t)h * (dim + rot) + d]
+                                           : (d < dim + rot ? q_abs[((size_t)t * heads + h) * width + rank + d - dim] : zero);
+    }
+}
+
+RB_EXPORT int rb_latent_expand_query(const void* q, int ldq, const void* q_abs, int width, int rank, void* qx, int heads,
+                                     int dim, int rot, int head, int T, cudaStream_t st) {
+    if (T <= 0) return 0;
+    return rb_launch_pdl(latent_expand_query_kernel, dim3(T), dim3(256), 0, st, (const bf16*)q, ldq, (const bf16*)q_abs, width,
+                         rank, (bf16*)qx, heads, dim, rot, head);
+}
+
+// The values of the tokens that ran in the expanded form (segments of several tokens) into the rows that the output
+// projection reads: out[t, h * vdim + e] = ox[t, h * head + e]; rows of single tokens are another kernel's.
+__global__ void latent_take_values_kernel(const bf16* __restrict__ ox, const int* __restrict__ tok_seg,
+                                          const int* __restrict__ cu_q, bf16* __restrict__ out, int heads, int vdim, int head) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int seg = tok_seg[t];
+    if (cu_q[seg + 1] - cu_q[seg] <= 1) return;
+    for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) {
+        const int h = e / vdim, d = e - h * vdim;
+        out[(size_t)t * heads * vdim + e] = ox[((size_t)t * heads + h) * head + d];
+    }
+}
+
+RB_EXPORT int rb_latent_take_values(const void* ox, const int* tok_seg, const int* cu_q, void* out, int heads, int vdim,
+                                    int head, int T, cudaStream_t st) {
+    if (T <= 0) return 0;
+    return rb_launch_pdl(latent_take_values_kernel, dim3(T), dim3(256), 0, st, (const bf16*)ox, tok_seg, cu_q, (bf16*)out, heads,
+                         vdim, head);
+}
+
+// out[i, :] = x[index[i], :] for rows of `bytes` bytes (a multiple of 16), 16 bytes a thread and step.
+__global__ void latent_gather_rows_kernel(const unsigned char* __restrict__ x, long long ldx_bytes, const int* __restrict__ index,
+                                          unsigned char* __restrict__ out, int bytes) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const unsigned char* src = x + (size_t)index[blockIdx.x] * ldx_bytes;
+    unsigned char* dst = out + (size_t)blockIdx.x * bytes;
+    for (int b = threadIdx.x * 16; b < bytes; b += blockDim.x * 16)
+        *reinterpret_cast<uint4*>(dst + b) = *reinterpret_cast<const uint4*>(src + b);
+}
+
+RB_EXPORT int rb_latent_gather_rows(const void* x, long long ldx_bytes, const int* index, void* out, int bytes, int n,
+                                    cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (bytes % 16 || ldx_bytes % 16 || ((uintptr_t)x % 16) || ((uintptr_t)out % 16)) return (int)cudaErrorInvalidValue;
+    return rb_launch_pdl(latent_gather_rows_kernel, dim3(n), dim3(64), 0, st, (const unsigned char*)x, ldx_bytes, index,
+                         (unsigned char*)out, bytes);
+}

@@ -999,7 +999,13 @@ def latent_lib() -> ctypes.CDLL:
         lib.rb_latent_attention_simt.argtypes = [P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, P]
         lib.rb_head_gate.argtypes = [P, P, I, I, I, I, I, P]
         lib.rb_gemm_f32_heads.argtypes = [P, P, P, I, I, I, I, I, I, I, L, L, L, P]
-        for name in ("rb_latent_write", "rb_latent_attention_simt", "rb_head_gate", "rb_gemm_f32_heads"):
+        lib.rb_latent_expand_scatter.argtypes = [P, I, P, I, I, I, P, I, P, P, I, I, I, I, I, P]
+        lib.rb_latent_expand_query.argtypes = [P, I, P, I, I, P, I, I, I, I, I, P]
+        lib.rb_latent_take_values.argtypes = [P, P, P, P, I, I, I, I, P]
+        lib.rb_latent_gather_rows.argtypes = [P, L, P, P, I, I, P]
+        lib.rb_latent_gather_rows.restype = c_int
+        for name in ("rb_latent_write", "rb_latent_attention_simt", "rb_head_gate", "rb_gemm_f32_heads",
+                     "rb_latent_expand_scatter", "rb_latent_expand_query", "rb_latent_take_values"):
             getattr(lib, name).restype = c_int
         _latent = lib
     return _latent
@@ -1067,6 +1073,47 @@ def latent_attention(q_abs, pool, batch, block_table, page_size: int, sink, out,
         paged_attention(q_abs, as_heads, as_heads, batch, block_table, page_size, out, heads, 1, width, scale, window, sink)
         return
     latent_attention_simt(q_abs, pool, batch, block_table, page_size, sink, out, heads, rank, rot, scale, window)
+
+
+def gather_rows(x, index, out) -> None:
+    """out[i] = x[index[i]] for rows of whole 16-byte pieces (x [rows, K] with any row stride, out contiguous)."""
+    n, K = out.shape
+    assert x.dtype == out.dtype and x.stride(1) == 1 and out.is_contiguous() and x.shape[1] == K
+    assert index.dtype == torch.int32 and index.numel() == n
+    size = x.element_size()
+    _check(latent_lib().rb_latent_gather_rows(_ptr(x), x.stride(0) * size, _ptr(index), _ptr(out), K * size, n, _stream()),
+           "gather_rows")
+
+
+def latent_expand_scatter(kv, lat, rank: int, rot: int, slots, page_size: int, kx, vx, heads: int, dim: int, vdim: int) -> None:
+    """Row i of ``kv`` ([U; V] applied to gathered latent i: heads x dim key numbers, then heads x vdim value numbers)
+    and the rotated part of ``lat`` row i into the scratch pools kx, vx [pages, heads, page_size, head] at
+    slots[i] = page * page_size + row: key [U_h c | rotated part | 0], value [V_h c | 0]."""
+    n = slots.numel()
+    head = kx.shape[-1]
+    assert kv.dtype == lat.dtype == kx.dtype == vx.dtype == torch.bfloat16 and kv.stride(1) == 1 and lat.stride(1) == 1
+    assert kx.is_contiguous() and vx.is_contiguous() and kx.shape == vx.shape and kx.shape[1] == heads and kx.shape[2] == page_size
+    assert kv.shape == (n, heads * (dim + vdim)) and lat.shape[0] == n and slots.dtype == torch.int32
+    _check(latent_lib().rb_latent_expand_scatter(_ptr(kv), kv.stride(0), _ptr(lat), lat.stride(0), rank, rot, _ptr(slots),
+                                                 page_size, _ptr(kx), _ptr(vx), heads, dim, vdim, head, n, _stream()),
+           "latent_expand_scatter")
+
+
+def latent_expand_query(q, q_abs, width: int, rank: int, qx, heads: int, dim: int, rot: int) -> None:
+    """qx[t, h] = [q[t, h, :dim] | the rotated part that lies in q_abs[t, h, rank : rank + rot] | 0]."""
+    T = q.shape[0]
+    head = qx.shape[1] // heads
+    assert q.dtype == q_abs.dtype == qx.dtype == torch.bfloat16 and q.stride(1) == 1 and q_abs.is_contiguous() and qx.is_contiguous()
+    _check(latent_lib().rb_latent_expand_query(_ptr(q), q.stride(0), _ptr(q_abs), width, rank, _ptr(qx), heads, dim, rot, head,
+                                               T, _stream()), "latent_expand_query")
+
+
+def latent_take_values(ox, batch, out, heads: int, vdim: int) -> None:
+    """out[t, h * vdim + e] = ox[t, h * head + e] for the tokens of segments of several tokens."""
+    T = out.shape[0]
+    assert ox.is_contiguous() and out.is_contiguous() and ox.dtype == out.dtype == torch.bfloat16
+    _check(latent_lib().rb_latent_take_values(_ptr(ox), _ptr(batch.tok_seg), _ptr(batch.cu_q), _ptr(out), heads, vdim,
+                                              ox.shape[1] // heads, T, _stream()), "latent_take_values")
 
 
 def head_gate(x, gate, heads: int) -> None:

@@ -85,6 +85,7 @@ class KVView:
     v: Optional[torch.Tensor]         # None for a LatentCacheNeed
     block_table: torch.Tensor         # int32 [segments of the step, blocks]
     page_size: int
+    group: int = -1                   # which of the cache manager's groups: batch.host.block_tables[group] is the host's twin
 
 
 @dataclass

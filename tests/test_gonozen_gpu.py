@@ -507,6 +507,34 @@ def test_widths_that_pick_the_other_attention_kernels(tmp_path_factory, dtype):
         assert_close(graphed["r0"], want0[[0, 500, 1099] + list(range(1100, 1200))], dtype, "long, graphs")
 
 
+def written_out_config():
+    """Heads whose keys and values, written out, are narrower than a cached vector (64 against 96, 128 against 192): in
+    bfloat16 portions of prompts then run with keys and values expanded per head while single tokens run over the cached
+    vectors themselves, side by side in one step."""
+    return config([windowed_layer(heads=3, dim=64, vdim=48, kv_rank=96, q_rank=40, window=50, mlp=None),
+                   rotated_layer(heads=2, dim=96, rot_dim=32, vdim=128, kv_rank=160, mlp=None),
+                   rotated_layer(heads=4, dim=24, rot_dim=8, vdim=64, kv_rank=80, scaling=False)], width=64)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_with_keys_and_values_written_out(tmp_path_factory, dtype, monkeypatch):
+    from return_b200.ext import ops
+    entry = model(tmp_path_factory, "written_out", written_out_config(), seed=9)
+    reqs = requests_for(entry, (120, 47, 70, 9), seed=60)
+    calls, scatter = [], ops.latent_expand_scatter
+    monkeypatch.setattr(ops, "latent_expand_scatter", lambda *a, **k: (calls.append(1), scatter(*a, **k))[1])
+    compare(entry, dtype, whole(reqs), reqs)
+    assert len(calls) == (4 * 3 if dtype == "bfloat16" else 0)     # four prompts, three layers; never in float32
+    compare(entry, dtype, tail_decoded(reqs, tail=30), reqs, page_size=8)
+    compare(entry, dtype, portions(reqs, [2, 49, 3, 51, 17]), reqs, page_size=4)
+    compare(entry, dtype, mixed(reqs, max_live=3, portion=21, decode_tail=7, seed=4), reqs, page_size=16)
+    long = requests_for(entry, (1250,), seed=61)
+    steps = [{"step": 0, "entries": [{"id": "r0", "tokens": long["r0"][:1150], "want": [0, 1149]}], "end": []},
+             {"step": 1, "entries": [{"id": "r0", "tokens": long["r0"][1150:], "want": list(range(100))}], "end": ["r0"]}]
+    got = run_trace(entry[0], dtype, steps)                        # a short portion behind a long prefix: keys shared out and merged
+    assert_close(got["r0"], plain_rows(entry, long["r0"])[[0, 1149] + list(range(1150, 1250))], dtype, "long prefix")
+
+
 # ------------------------------------------------------------------------------- generation through the engine
 
 def _greedy_plain(entry, prompt, n):
